@@ -35,6 +35,7 @@ struct RopeStoreArgs {
     int rows, heads, kv_heads, head_dim, rotary_dim;
     float eps;
     int transform;             // 0: only copy the k and v heads, as they are, to the cache
+    int value_dim;             // width of a v head (0: head_dim); the v heads follow the k heads in a row
 };
 
 // One warp per (row, head) over heads + 2*kv_heads heads.
@@ -51,7 +52,11 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
     if (seq < 0) return;
     const int position = a.row_pos[row];
     const int d = a.head_dim;
-    T* vector = (T*)a.qkv + row * a.ld + (long long)head * d;
+    const int vd = a.value_dim ? a.value_dim : d;
+    const bool is_value = head >= a.heads + a.kv_heads;
+    T* vector = (T*)a.qkv + row * a.ld +
+                (is_value ? (long long)(a.heads + a.kv_heads) * d + (long long)(head - a.heads - a.kv_heads) * vd
+                          : (long long)head * d);
 
     // Where this head goes in the cache, if anywhere.
     T* cached = nullptr;
@@ -62,16 +67,16 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
             keep = position >= a.seq_start[seq] + a.seq_len[seq] - ring_tokens;
         }
         if (keep) {
-            const bool is_key = head < a.heads + a.kv_heads;
-            const int kv_head = is_key ? head - a.heads : head - a.heads - a.kv_heads;
-            cached = (T*)(is_key ? a.k_cache : a.v_cache) +
-                     cache_row_offset(a.cache, a.seq_slot[seq], position, kv_head);
+            const int kv_head = is_value ? head - a.heads - a.kv_heads : head - a.heads;
+            const long long offset = cache_row_offset(a.cache, a.seq_slot[seq], position, kv_head);
+            cached = is_value ? (T*)a.v_cache + offset / d * vd : (T*)a.k_cache + offset;
         }
     }
 
-    if (head >= a.heads + a.kv_heads || !a.transform) {  // a value head, or copy only
+    if (is_value || !a.transform) {  // a value head, or copy only
+        const int width = is_value ? vd : d;
         if (cached)
-            for (int c = lane; c < d; c += 32) cached[c] = vector[c];
+            for (int c = lane; c < width; c += 32) cached[c] = vector[c];
         return;
     }
 
@@ -230,10 +235,11 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, i
 KIDI_API int kidi_rope_store(const RopeStoreArgs* args, int dtype, int norm_dtype, cudaStream_t stream) {
     const RopeStoreArgs& a = *args;
     if (a.rows <= 0) return 0;
-    if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1)) return KIDI_REFUSED_SIZE;
+    if (a.head_dim > 256 || a.head_dim <= 0 || a.rotary_dim > a.head_dim || (a.rotary_dim & 1) || a.value_dim < 0)
+        return KIDI_REFUSED_SIZE;
     const long long items = (long long)a.rows * (a.heads + 2 * a.kv_heads);
     const unsigned blocks = (unsigned)((items + 3) / 4);
-    const bool vectors = dtype == KIDI_BF16 && items < (1LL << 30) && !((uintptr_t)a.q_norm & 15) &&
+    const bool vectors = dtype == KIDI_BF16 && items < (1LL << 30) && (!a.value_dim || a.value_dim == a.head_dim) && !((uintptr_t)a.q_norm & 15) &&
                          !((uintptr_t)a.k_norm & 15) && !(a.head_dim & 7) && !(a.ld & 7) && !((uintptr_t)a.qkv & 15) &&
                          !((uintptr_t)a.k_cache & 15) && !((uintptr_t)a.v_cache & 15) &&
                          (!a.cos_table || (!(a.rotary_dim & 15) && !((uintptr_t)a.cos_table & 15) &&
@@ -276,6 +282,11 @@ struct AttentionArgs {
     float scale;
     float softcap;        // > 0: a score s becomes softcap * tanh(s / softcap)
     const float* slopes;  // [heads] or null: head h adds slopes[h] * (key position - query position) to a score
+    int value_dim;        // width of a value head and of a head of `out` (0: head_dim), at most 256
+    const float* sinks;   // [heads] or null: exp(sinks[h]) is added to head h's softmax denominator (a key that
+                          // every row sees, with that score as it is, unscaled, and no value)
+    const void* gate;     // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
+    long long ldg;
 };
 
 // One block of 4 warps per (row, head). Warp w takes keys lo+w, lo+w+4, ... in
@@ -290,10 +301,11 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
     const int row = blockIdx.x, head = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d = a.head_dim;
-    T* out = (T*)a.out + row * a.ldo + (long long)head * d;
+    const int vd = a.value_dim ? a.value_dim : d;
+    T* out = (T*)a.out + row * a.ldo + (long long)head * vd;
     const int seq = a.row_seq[row];
     if (seq < 0) {
-        for (int c = threadIdx.x; c < d; c += 128) out[c] = from_float<T>(0.f);
+        for (int c = threadIdx.x; c < vd; c += 128) out[c] = from_float<T>(0.f);
         return;
     }
     const int position = a.row_pos[row];
@@ -313,13 +325,13 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
     for (int u = first + warp; u <= position; u += 4) {
         const T *key, *value;
         if (u >= start) {
-            const long long offset = (long long)(row0 + u - start) * a.ldkv + (long long)kv_head * d;
-            key = (const T*)a.k_step + offset;
-            value = (const T*)a.v_step + offset;
+            const long long offset = (long long)(row0 + u - start) * a.ldkv;
+            key = (const T*)a.k_step + offset + (long long)kv_head * d;
+            value = (const T*)a.v_step + offset + (long long)kv_head * vd;
         } else {
             const long long offset = cache_row_offset(a.cache, slot, u, kv_head);
             key = (const T*)a.k_cache + offset;
-            value = (const T*)a.v_cache + offset;
+            value = (const T*)a.v_cache + offset / d * vd;
         }
         float dot = 0.f;
 #pragma unroll
@@ -337,7 +349,7 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int c = lane + 32 * i;
-            if (c < d) acc[i] = acc[i] * keep + weight * to_float(value[c]);
+            if (c < vd) acc[i] = acc[i] * keep + weight * to_float(value[c]);
         }
         best = next;
     }
@@ -345,30 +357,37 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(AttentionArgs a)
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int c = lane + 32 * i;
-        if (c < d) part_acc[warp][c] = acc[i];
+        if (c < vd) part_acc[warp][c] = acc[i];
     }
     __syncthreads();
     float top = part_max[0];
 #pragma unroll
     for (int w = 1; w < 4; ++w) top = fmaxf(top, part_max[w]);
-    float total = 0.f, factor[4];
+    const float sink = a.sinks ? a.sinks[head] : -INFINITY;
+    top = fmaxf(top, sink);
+    float total = a.sinks ? expf(sink - top) : 0.f, factor[4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
         factor[w] = part_max[w] == -INFINITY ? 0.f : expf(part_max[w] - top);
         total += part_sum[w] * factor[w];
     }
-    for (int c = threadIdx.x; c < d; c += 128) {
+    float gate = 1.f;
+    if (a.gate) gate = 1.0f / (1.0f + expf(-to_float(((const T*)a.gate)[row * a.ldg + head])));
+    for (int c = threadIdx.x; c < vd; c += 128) {
         float value = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) value += part_acc[w][c] * factor[w];
-        out[c] = from_float<T>(value / total);
+        value /= total;
+        out[c] = from_float<T>(a.gate ? value * gate : value);
     }
 }
 
 KIDI_API int kidi_attention_generic(const AttentionArgs* args, int dtype, cudaStream_t stream) {
     const AttentionArgs& a = *args;
     if (a.rows <= 0) return 0;
-    if (a.head_dim > 256 || a.head_dim <= 0 || a.heads % a.kv_heads || a.heads > 65535) return KIDI_REFUSED_SIZE;
+    if (a.head_dim > 256 || a.head_dim <= 0 || a.heads % a.kv_heads || a.heads > 65535 || a.value_dim < 0 ||
+        a.value_dim > 256)
+        return KIDI_REFUSED_SIZE;
     dim3 grid(a.rows, a.heads);
     if (dtype == KIDI_F32) return kidi_launch(attention_generic_kernel<float>, grid, 128, 0, stream, a);
     if (dtype == KIDI_BF16) return kidi_launch(attention_generic_kernel<bf16>, grid, 128, 0, stream, a);

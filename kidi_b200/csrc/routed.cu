@@ -1,10 +1,13 @@
-// A feed-forward made of many small gated experts, of which each token uses a few.
+// A feed-forward made of many small experts, of which each token uses a few.
 //
-//   z = W_router h (32-bit), s = score(z); the `top` experts with the largest scores are taken
-//   (ties: the lower index) with weights w = s (optionally divided by their sum);
+//   z = W_router h (32-bit), s = score(z), a sigmoid of each logit or a softmax over all of them; the `top`
+//   experts with the largest scores are taken (ties: the lower index) with weights w = s (optionally divided
+//   by their sum plus a small number). With groups, the experts form equal runs of neighbours, a group's
+//   score is its largest, and only experts of the `keep` best groups (ties: the lower index) can be taken;
 //   y = sum over the chosen experts of  scale_out * W_down[e] (act(W_gate[e] x) * (W_up[e] x)),
 //   x = scale_in * h, where the weight w is scale_in (a weight on the expert's input) or scale_out
-//   (on its output) and the other is 1. act is SiLU.
+//   (on its output) and the other is 1. act is SiLU. An expert without a gate is W_down[e] gelu(W_up[e] x)
+//   with the exact gelu, 0.5 z (1 + erf(z / sqrt 2)).
 //
 // A (row, choice) pair is a "slot": slot = row * top + choice.
 //
@@ -55,22 +58,72 @@ __device__ __forceinline__ float dot1<bf16, bf16>(const bf16* __restrict__ w, co
 template <typename T, typename TW>
 __global__ void __launch_bounds__(512) route_kernel(const T* __restrict__ x, const TW* __restrict__ router,
                                                     int* __restrict__ chosen, float* __restrict__ weight, int hidden,
-                                                    int experts, int top, int renormalise) {
-    extern __shared__ float score[];
+                                                    int experts, int top, int renormalise, int softmax, int groups,
+                                                    int keep, float renormalise_eps) {
+    extern __shared__ float score[];       // [experts] scores, then [experts] what may still be chosen
+    float* open = score + experts;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long row = blockIdx.x;
     for (int e = warp; e < experts; e += 16) {
         const float z = warp_sum(dot1<T, TW>(router + (long long)e * hidden, x + row * hidden, hidden, lane));
-        if (lane == 0) score[e] = 1.0f / (1.0f + expf(-z));
+        if (lane == 0) score[e] = softmax ? z : 1.0f / (1.0f + expf(-z));
     }
     __syncthreads();
     if (warp) return;
+    if (softmax) {                         // over all experts, the sum in lane order and then across the lanes
+        float most = -INFINITY;
+        for (int e = lane; e < experts; e += 32) most = fmaxf(most, score[e]);
+        most = warp_max(most);
+        float sum = 0.f;
+        for (int e = lane; e < experts; e += 32) sum += expf(score[e] - most);
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) score[e] = expf(score[e] - most) / sum;
+        __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32) open[e] = score[e];
+    __syncwarp();
+    if (groups > 1 && keep < groups) {
+        // The best `keep` groups stay open: one after the other the group with the largest best score is marked,
+        // then every expert of an unmarked group is closed. A lane looks after groups lane, lane + 32, ...
+        const int per = experts / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float best = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, score[e]);
+            // a group's best score is kept in its first expert's `open` entry while the groups are ranked
+            open[g * per] = best;
+        }
+        __syncwarp();
+        unsigned long long kept_low = 0ull;      // groups kept by this lane, bit j for group lane + 32 j
+        for (int k = 0; k < keep; ++k) {
+            float best = -INFINITY;
+            int at = 0x7fffffff;
+            for (int g = lane, j = 0; g < groups; g += 32, ++j) {
+                if (kept_low >> j & 1ull) continue;
+                const float s = open[g * per];
+                if (s > best) { best = s; at = g; }
+            }
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) {
+                const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+                const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
+                if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
+            }
+            if (at == 0x7fffffff) break;
+            if ((at & 31) == lane) kept_low |= 1ull << (at >> 5);
+        }
+        __syncwarp();
+        for (int g = lane, j = 0; g < groups; g += 32, ++j) {
+            const bool kept = kept_low >> j & 1ull;
+            for (int e = g * per; e < (g + 1) * per; ++e) open[e] = kept ? score[e] : -INFINITY;
+        }
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
         int at = 0x7fffffff;
         for (int e = lane; e < experts; e += 32) {
-            const float s = score[e];
+            const float s = open[e];
             if (s > best) { best = s; at = e; }          // ascending e: the first of equals stays
         }
 #pragma unroll
@@ -79,27 +132,31 @@ __global__ void __launch_bounds__(512) route_kernel(const T* __restrict__ x, con
             const int other_at = __shfl_xor_sync(0xffffffffu, at, offset);
             if (other > best || (other == best && other_at < at)) { best = other; at = other_at; }
         }
-        if (at == 0x7fffffff) at = k;                     // every score left is a NaN
+        if (at == 0x7fffffff) { at = k; best = score[k]; }   // every score left is a NaN or closed
         if (lane == 0) {
             chosen[row * top + k] = at;
             weight[row * top + k] = best;
-            score[at] = -INFINITY;
+            open[at] = -INFINITY;
         }
         total += best;
         __syncwarp();
     }
-    if (renormalise && lane < top) weight[row * top + lane] /= total;
+    if (renormalise && lane < top) weight[row * top + lane] /= total + renormalise_eps;
 }
 
 KIDI_API int kidi_route(const void* x, int dtype, const void* router, int weight_dtype, int* chosen, float* weight,
-                        int rows, int hidden, int experts, int top, int renormalise, cudaStream_t stream) {
+                        int rows, int hidden, int experts, int top, int renormalise, int softmax, int groups, int keep,
+                        float renormalise_eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (experts <= 0 || experts > 1024 || top <= 0 || top > experts || top > 32) return KIDI_REFUSED_SIZE;
-    const size_t shared = (size_t)experts * sizeof(float);
+    if (groups < 1 || experts % groups || keep < 1 || keep > groups || groups > 2048 ||
+        (long long)keep * (experts / groups) < top)
+        return KIDI_REFUSED_SIZE;
+    const size_t shared = (size_t)experts * 2 * sizeof(float);
 #define KIDI_CASE(D, T, W, TW)                                                                                        \
     if (dtype == D && weight_dtype == W)                                                                              \
         return kidi_launch(route_kernel<T, TW>, (unsigned)rows, 512, shared, stream, (const T*)x, (const TW*)router,  \
-                           chosen, weight, hidden, experts, top, renormalise);
+                           chosen, weight, hidden, experts, top, renormalise, softmax, groups, keep, renormalise_eps);
     KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
     KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
     KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
@@ -151,23 +208,24 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(128) expert_gate_up_kernel(const T* __restrict__ x, const TW* __restrict__ gate_up,
                                                              const int* __restrict__ chosen, const float* __restrict__ weight,
                                                              T* __restrict__ mid, long long slots, int top, int hidden,
-                                                             int inter, int weight_on_input) {
+                                                             int inter, int weight_on_input, int gated) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + warp;
     if (item >= slots * inter) return;
     const long long slot = item / inter;
     const int n = (int)(item - slot * inter);
     const int expert = chosen[slot];
-    const TW* base = gate_up + (long long)expert * 2 * inter * hidden;
+    const TW* base = gate_up + (long long)expert * (gated ? 2 : 1) * inter * hidden;
     const T* row = x + (slot / top) * hidden;
+    const long long second = gated ? inter + n : n;     // without a gate there is one row: both sums are the same
     float g = 0.f, u = 0.f;
     if constexpr (sizeof(T) == sizeof(TW)) dot2<T>((const T*)base + (long long)n * hidden,
-                                                   (const T*)base + (long long)(inter + n) * hidden, row, hidden, lane, g, u);
+                                                   (const T*)base + second * hidden, row, hidden, lane, g, u);
     else
         for (int k = lane; k < hidden; k += 32) {
             const float v = to_float(row[k]);
             g = fmaf(to_float(base[(long long)n * hidden + k]), v, g);
-            u = fmaf(to_float(base[(long long)(inter + n) * hidden + k]), v, u);
+            u = fmaf(to_float(base[second * hidden + k]), v, u);
         }
     g = warp_sum(g);
     u = warp_sum(u);
@@ -175,17 +233,19 @@ __global__ void __launch_bounds__(128) expert_gate_up_kernel(const T* __restrict
         const float w = weight_on_input ? weight[slot] : 1.f;
         g *= w;
         u *= w;
-        mid[slot * inter + n] = from_float<T>(g / (1.0f + expf(-g)) * u);
+        mid[slot * inter + n] = from_float<T>(gated ? g / (1.0f + expf(-g)) * u
+                                                    : 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)));
     }
 }
 
 // ---------------------------------------------------------- slots: down
-// down [experts, hidden, inter]; out [rows, hidden] = sum over a row's choices, in their order.
+// down [experts, hidden, inter]; out [rows, hidden] = sum over a row's choices, in their order (plus `addend`
+// [rows, hidden], if given: the result of an expert that every row passes).
 template <typename T, typename TW>
 __global__ void __launch_bounds__(128) expert_down_kernel(const T* __restrict__ mid, const TW* __restrict__ down,
                                                           const int* __restrict__ chosen, const float* __restrict__ weight,
                                                           T* __restrict__ out, long long rows, int top, int hidden, int inter,
-                                                          int weight_on_input) {
+                                                          int weight_on_input, const T* __restrict__ addend) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * 4 + warp;
     if (item >= rows * hidden) return;
@@ -203,12 +263,13 @@ __global__ void __launch_bounds__(128) expert_down_kernel(const T* __restrict__ 
         a = warp_sum(a);
         total += weight_on_input ? a : a * weight[slot];
     }
-    if (lane == 0) out[row * hidden + n] = from_float<T>(total);
+    if (lane == 0) out[row * hidden + n] = from_float<T>(addend ? total + to_float(addend[row * hidden + n]) : total);
 }
 
 KIDI_API int kidi_expert_slots(const void* x, int dtype, const void* gate_up, const void* down, int weight_dtype,
                                const int* chosen, const float* weight, void* mid, void* out, int rows, int top,
-                               int hidden, int inter, int weight_on_input, cudaStream_t stream) {
+                               int hidden, int inter, int weight_on_input, int gated, const void* addend,
+                               cudaStream_t stream) {
     if (rows <= 0) return 0;
     const long long slots = (long long)rows * top;
     const long long first = slots * inter, second = (long long)rows * hidden;
@@ -217,11 +278,11 @@ KIDI_API int kidi_expert_slots(const void* x, int dtype, const void* gate_up, co
     if (dtype == D && weight_dtype == W) {                                                                         \
         int status = kidi_launch(expert_gate_up_kernel<T, TW>, (unsigned)((first + 3) / 4), 128, 0, stream,       \
                                  (const T*)x, (const TW*)gate_up, chosen, weight, (T*)mid, slots, top, hidden,     \
-                                 inter, weight_on_input);                                                          \
+                                 inter, weight_on_input, gated);                                                   \
         if (status) return status;                                                                                 \
         return kidi_launch(expert_down_kernel<T, TW>, (unsigned)((second + 3) / 4), 128, 0, stream, (const T*)mid, \
                            (const TW*)down, chosen, weight, (T*)out, (long long)rows, top, hidden, inter,          \
-                           weight_on_input);                                                                       \
+                           weight_on_input, (const T*)addend);                                                     \
     }
     KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
     KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
@@ -250,7 +311,8 @@ __global__ void gather_slots_kernel(const T* __restrict__ x, const int* __restri
 // out[row] = sum over the row's choices k of y[place[row * top + k]] (* weight), in the order of the choices.
 template <typename T>
 __global__ void combine_slots_kernel(const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weight,
-                                     T* __restrict__ out, long long total, int top, int hidden, int weight_on_input) {
+                                     T* __restrict__ out, long long total, int top, int hidden, int weight_on_input,
+                                     const T* __restrict__ addend) {
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= total) return;
     const long long row = index / hidden;
@@ -261,6 +323,7 @@ __global__ void combine_slots_kernel(const T* __restrict__ y, const int* __restr
         const float value = to_float(y[(long long)place[slot] * hidden + c]);
         sum += weight_on_input ? value : value * weight[slot];
     }
+    if (addend) sum += to_float(addend[index]);
     out[index] = from_float<T>(sum);
 }
 
@@ -290,7 +353,7 @@ __global__ void gather_slots_bf16x8_kernel(const bf16* __restrict__ x, const int
 
 __global__ void combine_slots_bf16x8_kernel(const bf16* __restrict__ y, const int* __restrict__ place,
                                             const float* __restrict__ weight, bf16* __restrict__ out, long long groups,
-                                            int top, int hidden, int weight_on_input) {
+                                            int top, int hidden, int weight_on_input, const bf16* __restrict__ addend) {
     const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (index >= groups) return;
     const int per_row = hidden >> 3;
@@ -307,6 +370,16 @@ __global__ void combine_slots_bf16x8_kernel(const bf16* __restrict__ y, const in
             const float2 v = __bfloat1622float2(pairs[j]);
             sum[2 * j] += weight_on_input ? v.x : v.x * w;
             sum[2 * j + 1] += weight_on_input ? v.y : v.y * w;
+        }
+    }
+    if (addend) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(addend + row * hidden + c);
+        const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 v = __bfloat1622float2(pairs[j]);
+            sum[2 * j] += v.x;
+            sum[2 * j + 1] += v.y;
         }
     }
     uint4 result;
@@ -332,16 +405,17 @@ KIDI_API int kidi_gather_slots(const void* x, int dtype, const int* order, const
 }
 
 KIDI_API int kidi_combine_slots(const void* y, int dtype, const int* place, const float* weight, void* out, int rows,
-                                int top, int hidden, int weight_on_input, cudaStream_t stream) {
+                                int top, int hidden, int weight_on_input, const void* addend, cudaStream_t stream) {
     const long long total = (long long)rows * hidden;
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == KIDI_F32) return kidi_launch(combine_slots_kernel<float>, blocks, 256, 0, stream, (const float*)y, place,
-                                              weight, (float*)out, total, top, hidden, weight_on_input);
-    if (dtype == KIDI_BF16 && !(hidden & 7) && !((uintptr_t)y & 15) && !((uintptr_t)out & 15))
+                                              weight, (float*)out, total, top, hidden, weight_on_input, (const float*)addend);
+    if (dtype == KIDI_BF16 && !(hidden & 7) && !((uintptr_t)y & 15) && !((uintptr_t)out & 15) && !((uintptr_t)addend & 15))
         return kidi_launch(combine_slots_bf16x8_kernel, (unsigned)(((total >> 3) + 255) / 256), 256, 0, stream,
-                           (const bf16*)y, place, weight, (bf16*)out, total >> 3, top, hidden, weight_on_input);
+                           (const bf16*)y, place, weight, (bf16*)out, total >> 3, top, hidden, weight_on_input,
+                           (const bf16*)addend);
     if (dtype == KIDI_BF16) return kidi_launch(combine_slots_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)y, place,
-                                               weight, (bf16*)out, total, top, hidden, weight_on_input);
+                                               weight, (bf16*)out, total, top, hidden, weight_on_input, (const bf16*)addend);
     return KIDI_REFUSED_DTYPE;
 }

@@ -14,27 +14,51 @@ constexpr int ROW_THREADS = 256;
 
 // ---------------------------------------------------------------- residual add + layer norm
 // One block per output row r; source row s = row_index ? row_index[r] : r.
-//   v = residual[s] + delta[s] (delta optional); if write_residual: residual[s] = v
-//   y[r] = (v - mean(v)) / sqrt(mean((v - mean)^2) + eps) * w + b
+//   d = delta[s], or with delta_weight the delta's own layer norm without bias:
+//       d = (delta[s] - mean(delta[s])) / sqrt(mean((delta[s] - mean)^2) + delta_eps) * delta_weight
+//   v = residual[s] + d (delta optional); if write_residual: residual[s] = v
+//   y[r] = (v - mean(v)) / sqrt(mean((v - mean)^2) + eps) * w + b        (y optional: only the sum is formed)
 // The row is staged in shared memory; the variance is taken of the deviations (second pass).
 template <typename TD, typename TY>
 __global__ void __launch_bounds__(ROW_THREADS)
 add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, const float* __restrict__ weight,
                      const float* __restrict__ bias, TY* __restrict__ y, const int* __restrict__ row_index,
-                     int hidden, float eps, int write_residual) {
+                     int hidden, float eps, int write_residual, const float* __restrict__ delta_weight,
+                     float delta_eps) {
     extern __shared__ float staged[];
     __shared__ float scratch[32];
     const int r = blockIdx.x;
     const long long s = row_index ? row_index[r] : r;
     float* h = residual + s * hidden;
+    float delta_mean = 0.f, delta_inv = 1.f;
+    if (delta && delta_weight) {
+        float* d = staged + hidden;
+        float sum = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+            const float value = to_float(delta[s * hidden + c]);
+            d[c] = value;
+            sum += value;
+        }
+        delta_mean = block_sum<ROW_THREADS>(sum, scratch) / (float)hidden;
+        float square = 0.f;
+        for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
+            const float deviation = d[c] - delta_mean;
+            square = fmaf(deviation, deviation, square);
+        }
+        delta_inv = 1.0f / sqrtf(block_sum<ROW_THREADS>(square, scratch) / (float)hidden + delta_eps);
+    }
     float sum = 0.f;
     for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
         float value = h[c];
-        if (delta) value += to_float(delta[s * hidden + c]);
+        if (delta) {
+            if (delta_weight) value += (staged[hidden + c] - delta_mean) * delta_inv * delta_weight[c];
+            else value += to_float(delta[s * hidden + c]);
+        }
         if (write_residual) h[c] = value;
         staged[c] = value;
         sum += value;
     }
+    if (!y) return;
     const float mean = block_sum<ROW_THREADS>(sum, scratch) / (float)hidden;
     float square = 0.f;
     for (int c = threadIdx.x; c < hidden; c += ROW_THREADS) {
@@ -46,6 +70,45 @@ add_layernorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
     TY* out = y + (long long)r * hidden;
     for (int c = threadIdx.x; c < hidden; c += ROW_THREADS)
         out[c] = from_float<TY>((staged[c] - mean) * inv * weight[c] + (bias ? bias[c] : 0.f));
+}
+
+// ---------------------------------------------------------------- a gate per head; an activation; a vector on every row
+// x[r, h, :] *= sigmoid(gate[r, h]) for x [rows, heads, width] and gate logits [rows, heads] (row stride ldg);
+// the sigmoid and the product are 32-bit.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ x, long long ldx, const T* __restrict__ gate, long long ldg,
+                                 long long total, int heads, int width) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at >= total) return;
+    const int per_row = heads * width;
+    const long long row = at / per_row;
+    const int c = (int)(at - row * per_row);
+    const float g = to_float(gate[row * ldg + c / width]);
+    T* value = x + row * ldx + c;
+    *value = from_float<T>(to_float(*value) / (1.0f + expf(-g)));
+}
+
+// out = 0.5 z (1 + erf(z / sqrt 2)), element by element.
+template <typename T>
+__global__ void gelu_kernel(const T* __restrict__ z, T* __restrict__ out, long long total) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at >= total) return;
+    const float v = to_float(z[at]);
+    out[at] = from_float<T>(0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)));
+}
+
+// x *= factor, element by element (x 32-bit, in place).
+__global__ void scale_kernel(float* __restrict__ x, long long total, float factor) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at < total) x[at] *= factor;
+}
+
+// x[r, :] += vector (x 32-bit, in place).
+template <typename TW>
+__global__ void add_vector_kernel(float* __restrict__ x, const TW* __restrict__ vector, long long total, int hidden) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at >= total) return;
+    x[at] += to_float(vector[at % hidden]);
 }
 
 // ---------------------------------------------------------------- RMS norm of groups of plain rows
@@ -212,10 +275,13 @@ __global__ void add_cast_kernel(float* __restrict__ x, const TD* __restrict__ de
 
 KIDI_API int kidi_add_layernorm(float* residual, const void* delta, int delta_dtype, const float* weight,
                                 const float* bias, void* y, int y_dtype, const int* row_index, int rows, int hidden,
-                                float eps, int write_residual, cudaStream_t stream) {
+                                float eps, int write_residual, const float* delta_weight, float delta_eps,
+                                cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (delta_dtype == KIDI_NONE) { delta = nullptr; delta_dtype = KIDI_F32; }
-    const size_t shared = (size_t)hidden * sizeof(float);
+    if (y_dtype == KIDI_NONE) { y = nullptr; y_dtype = KIDI_F32; }
+    if (!delta) delta_weight = nullptr;
+    const size_t shared = (size_t)hidden * sizeof(float) * (delta_weight ? 2 : 1);
     if (hidden <= 0 || shared > 200 * 1024) return KIDI_REFUSED_SIZE;
 #define KIDI_CASE(D, TD, Y, TY)                                                                                    \
     if (delta_dtype == D && y_dtype == Y) {                                                                        \
@@ -225,13 +291,47 @@ KIDI_API int kidi_add_layernorm(float* residual, const void* delta, int delta_dt
             if (status != cudaSuccess) return (int)status;                                                         \
         }                                                                                                          \
         return kidi_launch(kernel, rows, ROW_THREADS, shared, stream, residual, (const TD*)delta, weight, bias,    \
-                           (TY*)y, row_index, hidden, eps, write_residual);                                        \
+                           (TY*)y, row_index, hidden, eps, write_residual, delta_weight, delta_eps);               \
     }
     KIDI_CASE(KIDI_F32, float, KIDI_F32, float)
     KIDI_CASE(KIDI_F32, float, KIDI_BF16, bf16)
     KIDI_CASE(KIDI_BF16, bf16, KIDI_F32, float)
     KIDI_CASE(KIDI_BF16, bf16, KIDI_BF16, bf16)
 #undef KIDI_CASE
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_head_gate(void* x, long long ldx, const void* gate, long long ldg, int dtype, int rows, int heads,
+                            int width, cudaStream_t stream) {
+    const long long total = (long long)rows * heads * width;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(head_gate_kernel<float>, blocks, 256, 0, stream, (float*)x, ldx,
+                                              (const float*)gate, ldg, total, heads, width);
+    if (dtype == KIDI_BF16) return kidi_launch(head_gate_kernel<bf16>, blocks, 256, 0, stream, (bf16*)x, ldx,
+                                               (const bf16*)gate, ldg, total, heads, width);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_gelu(const void* z, void* out, int dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(gelu_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, total);
+    if (dtype == KIDI_BF16) return kidi_launch(gelu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)z, (bf16*)out, total);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_scale(float* x, long long total, float factor, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    return kidi_launch(scale_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, total, factor);
+}
+
+KIDI_API int kidi_add_vector(float* x, const void* vector, int vector_dtype, int rows, int hidden, cudaStream_t stream) {
+    const long long total = (long long)rows * hidden;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (vector_dtype == KIDI_F32) return kidi_launch(add_vector_kernel<float>, blocks, 256, 0, stream, x, (const float*)vector, total, hidden);
+    if (vector_dtype == KIDI_BF16) return kidi_launch(add_vector_kernel<bf16>, blocks, 256, 0, stream, x, (const bf16*)vector, total, hidden);
     return KIDI_REFUSED_DTYPE;
 }
 

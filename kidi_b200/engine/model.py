@@ -68,6 +68,8 @@ class CausalLM:
                 raise invalid_argument(f"the schedule names layer {entry.layer}, which does not exist")
             if entry.cache_from is not None and not 0 <= entry.cache_from < index:
                 raise invalid_argument("a schedule entry may read the cache of an earlier entry only")
+            if entry.offset is not None and not hasattr(self.env.shared.get(entry.offset[0]), "add"):
+                raise invalid_argument(f"the schedule names stream offsets '{entry.offset[0]}', which do not exist")
         self.loaded = False
 
     # ------------------------------------------------------------------ tensors
@@ -132,7 +134,10 @@ class CausalLM:
         for index, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]
             options = {}
-            if getattr(layer, "supports_next_norm", False) and index + 1 < len(self.schedule):
+            if entry.offset is not None:
+                self.env.shared[entry.offset[0]].add(stream, entry.offset[1])
+            if getattr(layer, "supports_next_norm", False) and index + 1 < len(self.schedule) \
+                    and self.schedule[index + 1].offset is None:
                 # The norm that reads the stream next: the layer's last product may prepare its rows.
                 following = self.layers[self.schedule[index + 1].layer]
                 options["next_norm"] = following.first_norm() if hasattr(following, "first_norm") else None

@@ -223,7 +223,8 @@ def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_d
 
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None,
         step_rows_cached: bool = False, splits: Optional[int] = None, ring: Optional[bool] = None,
-        softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> None:
+        softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+        sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """`ctx` gives the step's `plan`, its device `tables` and `workspace(name, count, zero)`.
     `keys_in_step`: the step's own keys and values are read from qkv (else from the
     cache, like the earlier ones). `step_rows_cached`: they are in the cache as well (a cache
@@ -231,17 +232,21 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     from there. `rotation` (only where `fuses_rotation` said yes): dict(q_norm, k_norm, eps,
     cos, sin, rotary_dim, store): the kernel normalises and rotates q and the step's key
     and, with `store`, writes the step's key and value to the cache. `splits` and `ring`
-    override the launcher's own choice of the decode kernel's form (tests of each form)."""
+    override the launcher's own choice of the decode kernel's form (tests of each form).
+    `value_dim`, `sinks`, `gate`: value heads of another width than the keys, a number per head in the softmax
+    denominator, a sigmoid gate per row and head (see `ops.attention_generic`)."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
     # Scores that are bounded or shifted by position run on the general kernel (the tensor-core kernels
     # compute plain scaled scores).
     reshaped = bool(softcap) or slopes is not None
-    if (reshaped or not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode)
+    uneven = value_dim is not None and value_dim != head_dim
+    if (reshaped or uneven or sinks is not None or gate is not None
+            or not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode)
             or (kv_view is not None and kv_view.page_size != 64)):
         ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
                               window=window, tables=tables, kv_view=kv_view, keys_in_step=keys_in_step,
-                              softcap=softcap, slopes=slopes)
+                              softcap=softcap, slopes=slopes, value_dim=value_dim, sinks=sinks, gate=gate)
         return
     if not decode and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale):
         common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)

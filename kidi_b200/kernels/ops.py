@@ -157,7 +157,13 @@ def core():
         lib.kidi_advance_decode.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                             c_void_p]
         lib.kidi_add_layernorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                                           c_int, c_int, c_float, c_int, c_void_p]
+                                           c_int, c_int, c_float, c_int, c_void_p, c_float, c_void_p]
+        lib.kidi_head_gate.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p]
+        lib.kidi_gelu.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
+        lib.kidi_add_vector.argtypes = [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.kidi_scale.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
+        for name in ("kidi_head_gate", "kidi_gelu", "kidi_add_vector", "kidi_scale"):
+            getattr(lib, name).restype = c_int
         lib.kidi_rms_rows.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int,
                                       c_float, c_void_p]
         lib.kidi_poly_norm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p]
@@ -200,7 +206,8 @@ class RopeStoreArgs(ctypes.Structure):
                 ("cos_table", c_void_p), ("sin_table", c_void_p), ("row_seq", c_void_p), ("row_pos", c_void_p),
                 ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_len", c_void_p), ("k_cache", c_void_p),
                 ("v_cache", c_void_p), ("cache", CacheGeometry), ("rows", c_int), ("heads", c_int),
-                ("kv_heads", c_int), ("head_dim", c_int), ("rotary_dim", c_int), ("eps", c_float), ("transform", c_int)]
+                ("kv_heads", c_int), ("head_dim", c_int), ("rotary_dim", c_int), ("eps", c_float), ("transform", c_int),
+                ("value_dim", c_int)]
 
 
 class AttentionArgs(ctypes.Structure):
@@ -209,7 +216,8 @@ class AttentionArgs(ctypes.Structure):
                 ("out", c_void_p), ("ldo", c_longlong), ("row_seq", c_void_p), ("row_pos", c_void_p),
                 ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_row0", c_void_p), ("rows", c_int),
                 ("heads", c_int), ("kv_heads", c_int), ("head_dim", c_int), ("window", c_int), ("scale", c_float),
-                ("softcap", c_float), ("slopes", c_void_p)]
+                ("softcap", c_float), ("slopes", c_void_p), ("value_dim", c_int), ("sinks", c_void_p),
+                ("gate", c_void_p), ("ldg", c_longlong)]
 
 
 def cache_geometry(view, kv_heads: int, head_dim: int) -> CacheGeometry:
@@ -271,13 +279,16 @@ def _float_vector(vector: Optional[torch.Tensor], size: int, what: str) -> None:
         raise invalid_argument(f"{what} must be a contiguous float32 vector of {size} elements")
 
 
-def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
-                  bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: Optional[torch.Tensor],
+                  bias: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype],
+                  row_index: Optional[torch.Tensor] = None, delta_weight: Optional[torch.Tensor] = None,
+                  delta_eps: float = 0.0) -> Optional[torch.Tensor]:
     """residual += delta (in place, float32), then y = (v - mean) / sqrt(var + eps) * weight + bias over each
     row v of the residual. With `row_index`, row r of the output comes from row row_index[r] and the
-    residual is left as it is."""
-    _need_cuda(residual, delta, weight, bias, row_index)
+    residual is left as it is. With `delta_weight` the delta passes a layer norm of its own first (weight
+    `delta_weight`, no bias, `delta_eps`) and the normalised rows are what is added. With `out_dtype` None only
+    the sum is formed and nothing is returned."""
+    _need_cuda(residual, delta, weight, bias, row_index, delta_weight)
     if residual.dtype != torch.float32 or residual.dim() != 2 or not residual.is_contiguous():
         raise invalid_argument("the residual stream is a contiguous float32 matrix")
     hidden = residual.shape[1]
@@ -285,15 +296,61 @@ def add_layernorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight:
         raise invalid_argument("the residual delta must match the residual stream")
     _float_vector(weight, hidden, "the norm weight")
     _float_vector(bias, hidden, "the norm bias")
+    _float_vector(delta_weight, hidden, "the weight of the delta's norm")
+    if out_dtype is not None and weight is None:
+        raise invalid_argument("a layer norm needs its weight")
     if row_index is not None and (row_index.dtype != torch.int32 or row_index.dim() != 1):
         raise invalid_argument("row_index must be an int32 vector")
     rows = row_index.shape[0] if row_index is not None else residual.shape[0]
-    out = torch.empty((rows, hidden), dtype=out_dtype, device=residual.device)
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=residual.device) if out_dtype is not None else None
     _check(core().kidi_add_layernorm(
         _ptr(residual), _ptr(delta), dtype_code(delta.dtype) if delta is not None else NONE, _ptr(weight), _ptr(bias),
-        _ptr(out), dtype_code(out.dtype), _ptr(row_index), rows, hidden, float(eps),
-        0 if row_index is not None else 1, _stream()), "add_layernorm")
+        _ptr(out), dtype_code(out.dtype) if out is not None else NONE, _ptr(row_index), rows, hidden, float(eps),
+        0 if row_index is not None else 1, _ptr(delta_weight), float(delta_eps), _stream()), "add_layernorm")
     return out
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, heads: int, width: int) -> torch.Tensor:
+    """x[r, h, :] *= sigmoid(gate[r, h]) in place, for x [rows, heads * width] and gate logits [rows, heads] (views
+    whose last axis is contiguous); sigmoid and product in 32-bit."""
+    _need_cuda(x, gate)
+    rows = x.shape[0]
+    if x.shape != (rows, heads * width) or gate.shape != (rows, heads) or x.stride(1) != 1 or gate.stride(1) != 1 \
+            or gate.dtype != x.dtype:
+        raise invalid_argument("head_gate takes [rows, heads * width] and [rows, heads] of one type")
+    _check(core().kidi_head_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), dtype_code(x.dtype), rows, heads,
+                                 width, _stream()), "head_gate")
+    return x
+
+
+def gelu(z: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """0.5 z (1 + erf(z / sqrt 2)) element by element (the arithmetic is 32-bit); `out` may be z itself."""
+    _need_cuda(z, out)
+    if not z.is_contiguous() or (out is not None and (out.shape != z.shape or out.dtype != z.dtype or not out.is_contiguous())):
+        raise invalid_argument("gelu takes a contiguous tensor")
+    if out is None:
+        out = torch.empty_like(z)
+    _check(core().kidi_gelu(_ptr(z), _ptr(out), dtype_code(z.dtype), z.numel(), _stream()), "gelu")
+    return out
+
+
+def scale(x: torch.Tensor, factor: float) -> torch.Tensor:
+    """x *= factor in place (x float32, contiguous)."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise invalid_argument("scale takes a contiguous float32 tensor")
+    _check(core().kidi_scale(_ptr(x), x.numel(), float(factor), _stream()), "scale")
+    return x
+
+
+def add_vector(x: torch.Tensor, vector: torch.Tensor) -> None:
+    """x[r, :] += vector for every row of the float32 matrix x, in place."""
+    _need_cuda(x, vector)
+    if x.dtype != torch.float32 or x.dim() != 2 or not x.is_contiguous() or vector.shape != (x.shape[1],) \
+            or not vector.is_contiguous():
+        raise invalid_argument("add_vector takes a contiguous float32 matrix and a vector of its width")
+    _check(core().kidi_add_vector(_ptr(x), _ptr(vector), dtype_code(vector.dtype), x.shape[0], x.shape[1], _stream()),
+           "add_vector")
 
 
 def rms_rows(x: torch.Tensor, width: int, weight: Optional[torch.Tensor], eps: float,
@@ -501,14 +558,17 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 
 def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q_norm: Optional[torch.Tensor],
                k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
-               rotary_dim: int, tables, kv_view, store: bool, transform: bool = True) -> None:
-    """In place on qkv [rows, (heads + 2*kv_heads) * head_dim]: per-head RMSNorm and
-    rotation of the q and k heads; k and v heads are also written to the cache when
+               rotary_dim: int, tables, kv_view, store: bool, transform: bool = True,
+               value_dim: Optional[int] = None) -> None:
+    """In place on qkv [rows, (heads + kv_heads) * head_dim + kv_heads * value_dim (+ columns that are left
+    alone)]: per-head RMSNorm and rotation of the q and k heads; k and v heads are also written to the cache when
     `store` is set. With `transform=False` nothing is normalised or rotated: the k and v
-    heads are only copied to the cache. `tables` is the step's `DeviceTables`."""
+    heads are only copied to the cache. `tables` is the step's `DeviceTables`. `value_dim` (default head_dim) is
+    the width of a v head."""
     _need_cuda(qkv)
     rows = qkv.shape[0]
-    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or qkv.shape[1] < (heads + kv_heads) * head_dim + kv_heads * value_dim:
         raise invalid_argument("rope_store: qkv has the wrong shape")
     if (q_norm is None) != (k_norm is None):
         raise invalid_argument("rope_store: q_norm and k_norm come together")
@@ -526,24 +586,34 @@ def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q
         tables.seq_start.data_ptr(), tables.seq_len.data_ptr(),
         view.keys.data_ptr() if view is not None else 0, view.values.data_ptr() if view is not None else 0,
         cache_geometry(view, kv_heads, head_dim), rows, heads, kv_heads, head_dim, rotary_dim, float(eps),
-        1 if transform else 0)
+        1 if transform else 0, value_dim)
     _check(core().kidi_rope_store(ctypes.byref(args), dtype_code(qkv.dtype), dtype_code(norm_dtype), _stream()),
            "rope_store")
 
 
 def attention_generic(qkv: torch.Tensor, out: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int,
                       scale: float, window: Optional[int], tables, kv_view, keys_in_step: bool,
-                      softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> None:
+                      softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention of every row of the step over its sequence's keys. Keys of the
     step's own rows are read from `qkv` when `keys_in_step` is set, earlier ones (or
     all of them) from the cache. `softcap` > 0 bounds a score s to softcap * tanh(s / softcap);
-    `slopes` (float32 [heads]) adds slopes[h] * (key position - query position) to head h's scores."""
+    `slopes` (float32 [heads]) adds slopes[h] * (key position - query position) to head h's scores.
+    `value_dim` (default head_dim): the width of a value head and of a head of `out`. `sinks` (float32
+    [heads]): exp(sinks[h]) joins head h's softmax denominator. `gate` ([rows, heads], a view of the step's
+    element type): head h of a row is multiplied by sigmoid(gate[row, h])."""
+    value_dim = head_dim if value_dim is None else int(value_dim)
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.shape != (heads,) or not sinks.is_contiguous()
+                              or sinks.device != qkv.device):
+        raise invalid_argument("attention: the sinks must be a float32 vector with one entry per head")
+    if gate is not None and (gate.shape != (qkv.shape[0], heads) or gate.dtype != qkv.dtype or gate.stride(1) != 1):
+        raise invalid_argument("attention: the gate has one entry per row and head, in the rows' element type")
     if slopes is not None and (slopes.dtype != torch.float32 or slopes.shape != (heads,) or not slopes.is_contiguous()
                                or slopes.device != qkv.device):
         raise invalid_argument("attention: the score slopes must be a float32 vector with one entry per head")
     _need_cuda(qkv, out)
     rows = qkv.shape[0]
-    if out.shape != (rows, heads * head_dim) or out.dtype != qkv.dtype or out.stride(1) != 1:
+    if out.shape != (rows, heads * value_dim) or out.dtype != qkv.dtype or out.stride(1) != 1:
         raise invalid_argument("attention: the output has the wrong shape or type")
     if kv_view is None and not keys_in_step:
         raise invalid_argument("attention: there is neither a cache nor keys in the step")
@@ -556,7 +626,8 @@ def attention_generic(qkv: torch.Tensor, out: torch.Tensor, *, heads: int, kv_he
         cache_geometry(kv_view, kv_heads, head_dim), out.data_ptr(), out.stride(0),
         tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), tables.seq_slot.data_ptr(),
         tables.seq_start.data_ptr(), tables.seq_row0.data_ptr(), rows, heads, kv_heads, head_dim,
-        int(window or 0), float(scale), float(softcap or 0.0), slopes.data_ptr() if slopes is not None else 0)
+        int(window or 0), float(scale), float(softcap or 0.0), slopes.data_ptr() if slopes is not None else 0,
+        value_dim, _ptr(sinks), _ptr(gate), gate.stride(0) if gate is not None else 0)
     _check(core().kidi_attention_generic(ctypes.byref(args), dtype_code(qkv.dtype), _stream()), "attention")
 
 

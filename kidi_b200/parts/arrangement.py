@@ -128,3 +128,46 @@ class ParallelBlock(Part):
         if self.feed_forward is not None:
             ops.add_cast(stream.hidden, self.feed_forward.forward(normed, ctx), None)
         stream.add(mixed)
+
+
+@register_part("arrangement", "sandwich_norm")
+class SandwichNormBlock(Part):
+    """A norm before and a norm behind each sublayer:
+        x <- x + mixer_out_norm(mixer(input_norm(x)));  x <- x + feed_forward_out_norm(feed_forward(post_norm(x)))
+    The feed-forward (with its two norms) is optional. The norms behind the sublayers have a weight and no bias
+    (`delta_weight()`); a sublayer's result goes to the stream together with its norm, and the norm that reads the
+    stream next normalises the result, forms the 32-bit sum and normalises the sum in one kernel."""
+
+    ROLES = {"input_norm": "norm", "mixer": "mixer", "mixer_out_norm": "norm"}
+    OPTIONAL_ROLES = {"post_norm": "norm", "feed_forward": "feed_forward", "feed_forward_out_norm": "norm"}
+
+    def __init__(self, spec, env, parts: Dict[str, Part]):
+        super().__init__(spec, env)
+        self.input_norm = parts["input_norm"]
+        self.mixer = parts["mixer"]
+        self.mixer_out_norm = parts["mixer_out_norm"]
+        self.post_norm = parts.get("post_norm")
+        self.feed_forward = parts.get("feed_forward")
+        self.feed_forward_out_norm = parts.get("feed_forward_out_norm")
+        if len({self.post_norm is None, self.feed_forward is None, self.feed_forward_out_norm is None}) != 1:
+            raise invalid_argument("a sandwich block has a feed-forward with the norms before and behind it, or none")
+        for norm in (self.mixer_out_norm, self.feed_forward_out_norm):
+            if norm is not None and not hasattr(norm, "delta_weight"):
+                raise invalid_argument("the norm behind a sublayer must be one that a residual delta can pass")
+
+    def children(self):
+        return tuple(part for part in (self.input_norm, self.mixer, self.mixer_out_norm, self.post_norm,
+                                       self.feed_forward, self.feed_forward_out_norm) if part is not None)
+
+    def cache_requests(self) -> list:
+        return self.mixer.cache_requests()
+
+    def first_norm(self) -> Part:
+        return self.input_norm
+
+    def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool) -> None:
+        mixed = self.mixer.forward(plain_rows(self.input_norm.forward(stream)), ctx, views, owns_cache)
+        stream.add(mixed, normed_by=self.mixer_out_norm)
+        if self.feed_forward is not None:
+            result = self.feed_forward.forward(plain_rows(self.post_norm.forward(stream)), ctx)
+            stream.add(result, normed_by=self.feed_forward_out_norm)

@@ -18,6 +18,14 @@ slope * (key position - query position) to its scores; default none). The last t
 counterpart in the reference's Qwen3; they are there so that an architecture that bounds or
 shifts its scores is a specification, not a change to the kernels' arguments: such layers run
 on the general attention kernel in either precision.
+
+Three more, none of them in the reference's Qwen3: value_dim (the width of a value head, default
+head_dim: the output projection then takes num_heads * value_dim columns); sink (bool): a learned
+number per head, tensor `sink_name` [num_heads], whose exponential joins the softmax denominator
+(a key that every row sees, with that score as it is, unscaled, and no value); head_gate (bool):
+head h's result is multiplied by sigmoid(W_g x)_h, W_g the tensor `gate_name` [num_heads, hidden],
+its rows fused behind q, k and v into the one projection. Tensor names under the prefix are the
+parameters q_name, k_name, v_name, o_name, sink_name, gate_name.
 """
 from __future__ import annotations
 
@@ -52,12 +60,18 @@ class Attention(Part):
         self.out_bias = bool(spec.param("out_bias", False))
         self.eps = float(spec.param("qk_norm_eps", 1e-6))
         self.window = spec.param("window", None)
+        self.value_dim = int(spec.param("value_dim", self.head_dim))
+        self.has_sink = bool(spec.param("sink", False))
+        self.has_gate = bool(spec.param("head_gate", False))
+        self.names = {key: spec.param(key + "_name", default) for key, default in (
+            ("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"), ("o", "o_proj.weight"),
+            ("sink", "sinks"), ("gate", "gate_proj.weight"))}
         scale = spec.param("scale", None)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(self.head_dim))
         if self.hidden <= 0 or self.heads <= 0 or self.kv_heads <= 0 or self.heads % self.kv_heads or self.head_dim <= 0:
             raise invalid_argument("invalid attention dimensions")
-        if self.head_dim > 256:
-            raise unsupported(f"head_dim {self.head_dim} exceeds 256, the widest head the kernels take")
+        if self.head_dim > 256 or not 0 < self.value_dim <= 256:
+            raise unsupported(f"head widths {self.head_dim} and {self.value_dim}: the kernels take 1 to 256")
         if self.window is not None and int(self.window) <= 0:
             raise invalid_argument("an attention window must be positive")
         name = spec.param("position", None)
@@ -66,6 +80,12 @@ class Attention(Part):
             raise invalid_argument("the rotary encoding was built for another head width")
         self.q_width = self.heads * self.head_dim
         self.kv_width = self.kv_heads * self.head_dim
+        self.v_width = self.kv_heads * self.value_dim
+        self.out_width = self.heads * self.value_dim
+        # The fused projection's rows: q, k, v, then one gate row a head, then zero rows up to a multiple of 8
+        # (so that the rows of its result start on 16-byte boundaries).
+        self.fused_width = self.q_width + self.kv_width + self.v_width + (self.heads if self.has_gate else 0)
+        self.sinks = None
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
         self.q_norm = self.k_norm = None
@@ -84,12 +104,14 @@ class Attention(Part):
                                           slopes=self.slopes)
 
     def parameter_specs(self) -> List[ParamSpec]:
+        n = self.names
+        sources = [(n["q"], (self.q_width, self.hidden)), (n["k"], (self.kv_width, self.hidden)),
+                   (n["v"], (self.v_width, self.hidden))]
+        if self.has_gate:
+            sources.append((n["gate"], (self.heads, self.hidden)))
         specs = [
-            ParamSpec("qkv_proj.weight", (self.q_width + 2 * self.kv_width, self.hidden), sources=(
-                ("q_proj.weight", (self.q_width, self.hidden)),
-                ("k_proj.weight", (self.kv_width, self.hidden)),
-                ("v_proj.weight", (self.kv_width, self.hidden)))),
-            ParamSpec("o_proj.weight", (self.hidden, self.q_width)),
+            ParamSpec("qkv_proj.weight", (self.fused_width, self.hidden), sources=tuple(sources)),
+            ParamSpec(n["o"], (self.hidden, self.out_width)),
         ]
         if self.qkv_bias:
             specs.append(ParamSpec("qkv_proj.bias", (self.q_width + 2 * self.kv_width,), sources=(
@@ -99,18 +121,27 @@ class Attention(Part):
         if self.qk_norm:
             specs.append(ParamSpec("q_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
             specs.append(ParamSpec("k_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
+        if self.has_sink:
+            specs.append(ParamSpec(n["sink"], (self.heads,), init=("normal", 1.0)))
         return specs
 
     def bind(self, tensors) -> None:
-        self.qkv = Linear(tensors["qkv_proj.weight"], tensors.get("qkv_proj.bias"))
-        self.out = Linear(tensors["o_proj.weight"], tensors.get("o_proj.bias"))
+        fused = tensors["qkv_proj.weight"]
+        if self.fused_width % 8:
+            pad = torch.zeros((8 - self.fused_width % 8, self.hidden), dtype=fused.dtype, device=fused.device)
+            fused = torch.cat([fused, pad], dim=0).contiguous()
+        self.qkv = Linear(fused, tensors.get("qkv_proj.bias"))
+        self.out = Linear(tensors[self.names["o"]], tensors.get("o_proj.bias"))
         if self.qk_norm:
             self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+        if self.has_sink:
+            self.sinks = tensors[self.names["sink"]].float().contiguous()
 
     def cache_requests(self) -> list:
-        return [KVRequest(self.kv_heads, self.head_dim, int(self.window) if self.window is not None else None)]
+        return [KVRequest(self.kv_heads, self.head_dim, int(self.window) if self.window is not None else None,
+                          value_dim=self.value_dim if self.value_dim != self.head_dim else None)]
 
     def launch_signature(self, rows: int, longest: int) -> tuple:
         """The choices a captured decode step of `rows` sequences of at most `longest` tokens
@@ -124,8 +155,16 @@ class Attention(Part):
         position = self.position
         rotate = dict(cos=position.cos, sin=position.sin, rotary_dim=position.rotary_dim) if position is not None \
             else dict(cos=None, sin=None, rotary_dim=0)
-        common = dict(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim)
+        common = dict(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, value_dim=self.value_dim)
         ring = view.ring_pages > 0
+        extras = {}
+        if self.has_sink:
+            extras["sinks"] = self.sinks
+        if self.has_gate:
+            begin = self.q_width + self.kv_width + self.v_width
+            extras["gate"] = qkv[:, begin:begin + self.heads]
+        if self.value_dim != self.head_dim:
+            extras["value_dim"] = self.value_dim
         # A ring that is written before attention would lose keys that the step's
         # earlier rows still need; it is written afterwards unless the step is one
         # token per sequence. A full-history cache is written first.
@@ -134,16 +173,16 @@ class Attention(Part):
             raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
         # One token per sequence on the tensor-core path: the attention kernel takes the rows as
         # the projection left them and does norm, rotation and the cache write itself.
-        fused = owns_cache and store_first and self.launcher.fuses_rotation(plan, qkv, kv_view=view, q_norm=self.q_norm,
-                                                                            k_norm=self.k_norm, **rotate)
+        fused = owns_cache and store_first and not extras and self.launcher.fuses_rotation(
+            plan, qkv, kv_view=view, q_norm=self.q_norm, k_norm=self.k_norm, **rotate)
         if not fused:
             ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
                            store=store_first, **rotate, **common)
-        attended = torch.empty((qkv.shape[0], self.q_width), dtype=qkv.dtype, device=qkv.device)
+        attended = torch.empty((qkv.shape[0], self.out_width), dtype=qkv.dtype, device=qkv.device)
         keys_in_step = owns_cache and not plan.is_decode
         rotation = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, store=True, **rotate) if fused else None
         self.launcher.run(ctx, qkv, attended, kv_view=view, keys_in_step=keys_in_step, rotation=rotation,
-                          step_rows_cached=store_first and not fused)
+                          step_rows_cached=store_first and not fused, **extras)
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)

@@ -157,24 +157,41 @@ class ResidualStream:
     def __init__(self, hidden: torch.Tensor):
         self.hidden = hidden
         self.pending: Optional[torch.Tensor] = None
+        self.pending_norm = None      # a norm (with `delta_weight()`) that the pending delta passes before it is added
         self.prepared = None
         # Copies of the stream that a part keeps for later layers (role "stream_mix"): [n, rows, hidden]
         # float32, and how many of them are filled. `hidden` is then a view of one of them.
         self.kept: Optional[torch.Tensor] = None
         self.kept_count = 0
 
-    def add(self, delta: Optional[torch.Tensor]) -> None:
-        """`delta` None: the part that made it has added it through a sink already."""
+    def add(self, delta: Optional[torch.Tensor], normed_by=None) -> None:
+        """`delta` None: the part that made it has added it through a sink already. `normed_by`: a norm part
+        with `delta_weight()` (a layer norm without bias) that the delta passes before it is added; the norm
+        that reads the stream next does both in its kernel when it can (`take_pending_normed`)."""
         if delta is None:
             return
         if self.pending is not None:
             raise RuntimeError("a residual delta is pending already; a norm must take it first")
         self.pending = delta
+        self.pending_norm = normed_by
         self.prepared = None          # rows prepared before this delta are no longer the stream's
 
     def take_pending(self) -> Optional[torch.Tensor]:
-        delta, self.pending = self.pending, None
-        return delta
+        """The delta that the caller must add. A delta that still has to pass a norm of its own is normalised
+        and added here (a kernel of its own), so a caller that knows nothing of such deltas gets None."""
+        delta, norm = self.take_pending_normed()
+        if norm is None:
+            return delta
+        from ..kernels import ops
+        weight, eps = norm.delta_weight()
+        ops.add_layernorm(self.hidden, delta, None, None, 0.0, None, delta_weight=weight, delta_eps=eps)
+        return None
+
+    def take_pending_normed(self):
+        """(delta, norm): the pending delta and the norm it has to pass first (None: none)."""
+        delta, norm = self.pending, self.pending_norm
+        self.pending = self.pending_norm = None
+        return delta, norm
 
     def take_prepared(self, norm) -> Optional[tuple]:
         """(values, parts) if the stream's rows were prepared for `norm`, once."""

@@ -50,6 +50,7 @@ class LinearHead(Part):
         self.tied_to = spec.param("tied_to", None)
         self.name = spec.param("name", "weight")
         self.softcap = float(spec.param("softcap", 0.0) or 0.0)
+        self.logit_scale = float(spec.param("logit_scale", 1.0))     # the logits are multiplied by it, in 32-bit
         self.linear: Optional[Linear] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
@@ -60,4 +61,6 @@ class LinearHead(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         logits = self.linear.forward(x, out_dtype=torch.float32)
+        if self.logit_scale != 1.0:
+            logits = ops.scale(logits, self.logit_scale)
         return ops.tanh_cap(logits, self.softcap) if self.softcap > 0 else logits

@@ -64,7 +64,11 @@ class RMSNorm(Part):
 class LayerNorm(Part):
     """y = (x - mean(x)) / sqrt(mean((x - mean)^2) + eps) * w + b over each row, in 32-bit, in the kernel
     that also forms the residual sum. Parameters: size, eps, weight_name and bias_name (tensor names under
-    the prefix; default "weight" and "bias")."""
+    the prefix; default "weight" and "bias"), bias (default true; false: the norm has a weight only).
+
+    A norm without bias can also stand behind a sublayer, x <- x + norm(sublayer(...)): the arrangement hands
+    the sublayer's result to the stream with `normed_by=` this part, and the norm that reads the stream next
+    normalises the delta, adds it and normalises the sum in one kernel (`delta_weight`)."""
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -72,17 +76,31 @@ class LayerNorm(Part):
         self.eps = float(spec.param("eps"))
         self.weight_name = spec.param("weight_name", "weight")
         self.bias_name = spec.param("bias_name", "bias")
+        self.has_bias = bool(spec.param("bias", True))
         self.weight: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(self.weight_name, (self.size,), init=("one_plus_normal", 0.1)),
-                ParamSpec(self.bias_name, (self.size,), init=("normal", 0.1))]
+        specs = [ParamSpec(self.weight_name, (self.size,), init=("one_plus_normal", 0.1))]
+        if self.has_bias:
+            specs.append(ParamSpec(self.bias_name, (self.size,), init=("normal", 0.1)))
+        return specs
 
     def bind(self, tensors) -> None:
         self.weight = tensors[self.weight_name].float().contiguous()
-        self.bias = tensors[self.bias_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous() if self.has_bias else None
+
+    def delta_weight(self):
+        """(weight, eps) for a kernel that applies this norm to a residual delta before adding it."""
+        if self.has_bias:
+            raise RuntimeError("a norm behind a sublayer has no bias")
+        return self.weight, self.eps
 
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False):
-        return ops.add_layernorm(stream.hidden, stream.take_pending(), self.weight, self.bias, self.eps,
-                                 self.env.dtype, row_index=rows)
+        delta, delta_norm = stream.take_pending_normed()
+        weight, eps = delta_norm.delta_weight() if delta_norm is not None else (None, 0.0)
+        if rows is not None and delta is not None:
+            # Only some rows are wanted and the stream stays as it is: the delta goes back for whoever reads it next.
+            stream.pending, stream.pending_norm = delta, delta_norm
+        return ops.add_layernorm(stream.hidden, delta, self.weight, self.bias, self.eps, self.env.dtype,
+                                 row_index=rows, delta_weight=weight, delta_eps=eps)

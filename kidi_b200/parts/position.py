@@ -5,6 +5,15 @@ angle = float(position) * freq_i, cos and sin of it, all in 32-bit, positions fr
 0 (src/kidi/model/qwen3.cpp:138-157). A mixer that rotates its queries and keys looks
 the encoding up by name in `env.positions` and hands `cos`/`sin` to its kernel.
 
+With `scaling` = {factor, original, fast, slow} the table is stretched for sequences longer than the `original`
+length the frequencies were meant for (the scheme known as YaRN): pair i completes original * f_i / (2 pi) turns
+over that length; pairs that turn more often than `fast` keep their frequency, pairs that turn less often than
+`slow` have it divided by `factor`, and a linear ramp over the pair index blends between the two,
+    turns_to_pair(t) = n ln(original / (2 pi t)) / (2 ln theta),   n the rotary width
+    lo = max(floor(turns_to_pair(fast)), 0),  hi = min(ceil(turns_to_pair(slow)), n - 1)
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),   f_i <- f_i / factor * ramp_i + f_i (1 - ramp_i)
+and cosine and sine are both multiplied by 0.1 ln(factor) + 1.
+
 `learned_positions` is a table with a vector per position that is added to the embeddings
 (times `scale`, default 1), in 32-bit; mixers read nothing from it. Parameters: hidden_size,
 max_positions, scale, name (the table's tensor name under the prefix, default "weight").
@@ -32,6 +41,11 @@ class RotaryEncoding(Part):
         self.rotary_dim = int(spec.param("rotary_dim", self.head_dim))
         self.theta = float(spec.param("theta"))
         self.max_positions = int(spec.param("max_positions"))
+        scaling = spec.param("scaling", None)
+        self.scaling = {key: float(scaling[key]) for key in ("factor", "original", "fast", "slow")} if scaling else None
+        if self.scaling is not None and (self.scaling["factor"] <= 0 or self.scaling["original"] <= 0
+                                         or self.scaling["fast"] <= 0 or self.scaling["slow"] <= 0 or self.theta <= 1):
+            raise invalid_argument("a stretched rotary encoding needs positive constants and a base above 1")
         if self.rotary_dim <= 0 or self.rotary_dim % 2 or self.rotary_dim > self.head_dim:
             raise invalid_argument("the rotary width must be even and at most the head width")
         self._tables = None
@@ -48,9 +62,19 @@ class RotaryEncoding(Part):
             exponent = (2.0 * index) / torch.tensor(float(self.rotary_dim), dtype=torch.float32)
             power = torch.pow(torch.tensor(self.theta, dtype=torch.float32).double(), exponent.double()).float()
             frequency = 1.0 / power
+            factor = 1.0
+            if self.scaling is not None:
+                import math
+                s, n = self.scaling, float(self.rotary_dim)
+                pair = lambda turns: n * math.log(s["original"] / (2.0 * math.pi * turns)) / (2.0 * math.log(self.theta))
+                lo = max(math.floor(pair(s["fast"])), 0)
+                hi = min(math.ceil(pair(s["slow"])), self.rotary_dim - 1)
+                ramp = torch.clamp((index.double() - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+                frequency = (frequency.double() / s["factor"] * ramp + frequency.double() * (1.0 - ramp)).float()
+                factor = 0.1 * math.log(s["factor"]) + 1.0
             angle = torch.arange(self.max_positions, dtype=torch.float32)[:, None] * frequency[None, :]
-            self._tables = (torch.cos(angle).contiguous().to(self.env.device),
-                            torch.sin(angle).contiguous().to(self.env.device))
+            self._tables = ((torch.cos(angle) * factor).contiguous().to(self.env.device),
+                            (torch.sin(angle) * factor).contiguous().to(self.env.device))
         return self._tables
 
     @property

@@ -45,10 +45,12 @@ class ScheduleEntry:
     """One position in the run order. `layer` indexes `ModelSpec.layers` and may
     occur at several positions (shared weights; each position has a cache of its
     own). `cache_from` names an EARLIER position whose cache this one reads instead
-    of keeping one."""
+    of keeping one. `offset` = (name of a shared `stream_offsets` part, row): that row is added
+    to the stream right before this position's layer runs."""
 
     layer: int
     cache_from: Optional[int] = None
+    offset: Optional[Tuple[str, int]] = None
 
 
 @dataclasses.dataclass(frozen=True)

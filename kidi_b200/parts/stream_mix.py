@@ -67,3 +67,33 @@ class DepthAverage(Part):
         stream.hidden = mixed
         stream.kept_count = self.index + 2
         stream.prepared = None
+
+
+@register_part("shared", "stream_offsets")
+class StreamOffsets(Part):
+    """A table [count, hidden] of learned vectors of which the run order names one at some of its positions
+    (`ScheduleEntry.offset`): `add(stream, index)` adds row `index` to every row of the stream, in 32-bit, before
+    that position's layer runs: the vector that marks the pass of a range of layers that runs several times, say.
+    Parameters: hidden_size, count, name (the tensor's name, default "weight")."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.count = int(spec.param("count"))
+        self.name = spec.param("name", "weight")
+        if self.hidden <= 0 or self.count <= 0:
+            raise invalid_argument("a table of stream offsets needs a positive width and count")
+        self.table = None
+
+    def parameter_specs(self):
+        return [ParamSpec(self.name, (self.count, self.hidden), init=("normal", 0.1))]
+
+    def bind(self, tensors) -> None:
+        self.table = tensors[self.name]
+
+    def add(self, stream: ResidualStream, index: int) -> None:
+        if not 0 <= index < self.count:
+            raise invalid_argument(f"the run order names stream offset {index} of {self.count}")
+        # A delta that is still pending is added by the next norm; the order of the two additions does not matter.
+        stream.prepared = None
+        ops.add_vector(stream.hidden, self.table[index])

@@ -92,3 +92,4 @@ def _load_builtin() -> None:
         from .models import qwen3  # noqa: F401  (registers itself)
         from .models import sanozen  # noqa: F401
         from .models import gakenex  # noqa: F401
+        from .models import gazezen  # noqa: F401
