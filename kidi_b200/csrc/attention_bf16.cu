@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include <string.h>
 #include "attention_no_alloc.h"
 
 
@@ -136,7 +137,20 @@ struct Args {
     int rotary_dim;
     float eps;
     long long cache_rows;     // rows of head width in k_cache and in v_cache (pages * kv_heads * 64); 0: not told
+    const float* sinks;       // [heads] or null: exp(sinks[h]) joins head h's softmax denominator (a key that every
+                              // row sees, with that score as it is, unscaled, and no value)
+    const bf16* gate;         // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
+    long long ldg;
 };
+
+// What the weighted sum of a finished (row, head) is multiplied by: 1 / (denominator, with the head's sink in
+// it), times the row's gate. `top` is the maximum that the denominator `total` is relative to, in log2 units.
+__device__ __forceinline__ float finish_factor(const Args& a, long long row, int head, float top, float total) {
+    if (a.sinks) total += exp2f(a.sinks[head] * 1.4426950408889634f - top);
+    float factor = total > 0.f ? 1.0f / total : 0.f;
+    if (a.gate) factor *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[row * a.ldg + head])));
+    return factor;
+}
 
 // Loads one 64 x D tile of keys (or values) for absolute key positions [tile*64, tile*64+64)
 // of a sequence into padded shared memory. Positions >= step_from come from the step's
@@ -330,7 +344,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
     for (int half = 0; half < 2; ++half) {
         const int r = warp * 16 + g + half * 8;
         if (r >= q_rows) continue;
-        const float inverse = 1.0f / denom[half];
+        const float inverse = finish_factor(a, row0 + q0 + r, head, best[half], denom[half]);
         bf16* out = a.out + (long long)(row0 + q0 + r) * a.ldo + (long long)head * D;
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
@@ -460,7 +474,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
         const int head = head0 + r;
         if (a.splits == 1) {
             a.out[(long long)row * a.ldo + (long long)head * D + c] =
-                from_float<bf16>(total > 0.f ? value / total : 0.f);
+                from_float<bf16>(value * finish_factor(a, row, head, top, total));
         } else {
             const long long where = ((long long)row * a.heads + head) * a.splits + split;
             merged_out[where * D + c] = value;
@@ -988,8 +1002,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
         }
         const int head = head0 + r;
         if (a.splits == 1) {
-            const float total = merge_weight[32 + r * 2 + 1];
-            const float scale = total > 0.f ? 1.0f / total : 0.f;
+            const float scale = finish_factor(a, row, head, merge_weight[32 + r * 2], merge_weight[32 + r * 2 + 1]);
             bf16* out = a.out + (long long)row * a.ldo + (long long)head * D + c;
             *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(value.x * scale, value.y * scale);
             *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(value.z * scale, value.w * scale);
@@ -1026,7 +1039,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 const float4 part = *reinterpret_cast<const float4*>(recv_out + sp * share + i);
                 value.x += part.x * factor; value.y += part.y * factor; value.z += part.z * factor; value.w += part.w * factor;
             }
-            const float scale = total > 0.f ? 1.0f / total : 0.f;
+            const float scale = finish_factor(a, row, head0 + r, top, total);
             bf16* out = a.out + (long long)row * a.ldo + (long long)(head0 + r) * D + c;
             *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(value.x * scale, value.y * scale);
             *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(value.z * scale, value.w * scale);
@@ -1066,7 +1079,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 total += stat_factor[r * 32 + sp] * factor;
                 stat_factor[r * 32 + sp] = factor;
             }
-            stat_factor[8 * 32 + r] = total > 0.f ? 1.0f / total : 0.f;
+            stat_factor[8 * 32 + r] = finish_factor(a, row, head0 + r, top, total);
         }
         __syncthreads();
         for (int item = threadIdx.x; item < group * D; item += THREADS) {
@@ -1104,7 +1117,8 @@ __global__ void attention_combine_kernel(Args a) {
             total += a.partial_stat[(where + s) * 2 + 1] * factor;
             value += a.partial_out[(where + s) * D + c] * factor;
         }
-        a.out[(long long)row * a.ldo + (long long)head * D + c] = from_float<bf16>(total > 0.f ? value / total : 0.f);
+        a.out[(long long)row * a.ldo + (long long)head * D + c] =
+            from_float<bf16>(value * finish_factor(a, row, head, top, total));
     }
 }
 
@@ -1284,7 +1298,8 @@ KIDI_API long long kidi_attention_decode_static_need(int rows, int heads, int sp
 KIDI_API int kidi_attention_decode_static(const KidiAttentionArgs* args, cudaStream_t stream) {
     constexpr int MAX_DEVICES = 64;
     static std::atomic<float*> scratch_of_device[MAX_DEVICES];      // zero-initialised
-    Args a = *reinterpret_cast<const Args*>(args);
+    Args a = {};           // the public block ends before the sinks and the gate: they stay null
+    memcpy(&a, args, sizeof(KidiAttentionArgs));
     if (a.rows <= 0) return 0;
     const long long need = kidi_attention_decode_static_need(a.rows, a.heads, a.splits);
     if (need < 0 || a.heads <= 0) return KIDI_REFUSED_SIZE;

@@ -80,6 +80,9 @@ struct KidiAttentionArgs {
     float eps;
     long long cache_rows;          // pages * kv_heads * 64 when k_cache and v_cache are contiguous (pages are then
                                    // copied whole by TMA where the head width allows), else 0
+    const float* sinks;            // [heads] float32 or null: exp(sinks[h]) joins head h's softmax denominator
+    const void* gate;              // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
+    long long ldg;
 };
 
 // Bounds the static entry point checks before it forms the size of the workspace.

@@ -222,6 +222,10 @@ struct Params {
     const int* seq_start;   // [seqs] tokens in the cache before this step
     const int* seq_slot;    // [seqs]
     CacheGeometry cache;
+    const float* sinks;     // [heads] or null: exp(sinks[h]) joins head h's softmax denominator (a key that every
+                            // row sees, with that score as it is, unscaled, and no value)
+    const bf16* gate;       // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
+    long long ldg;
 };
 
 // Where a block works: its sequence, query rows, heads and key tiles.
@@ -564,7 +568,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, const 
                 float total = parts[0];
 #pragma unroll
                 for (int g = 1; g < GROUPS; ++g) total += parts[g];
-                const float inverse = 1.0f / total;
+                // The reference is the same in all warps of a row; the sink's exponential is taken against it.
+                if (p.sinks) total += exp2f(p.sinks[head0 + h] * LOG2E - (reference == -INFINITY ? 0.f : reference));
+                float inverse = 1.0f / total;
+                if (p.gate && r < q_rows)
+                    inverse *= 1.0f / (1.0f + expf(-__bfloat162float(p.gate[(long long)(row0 + q0 + r) * p.ldg + head0 + h])));
                 bf16* out = p.out + (long long)(row0 + q0 + r) * p.ldo + (long long)(head0 + h) * D;
 #pragma unroll 1
                 for (int c = 32 * group; c < D && ok; c += 32 * GROUPS) {
@@ -648,13 +656,19 @@ struct KidiPromptCache {     // where the keys and values lie when prompts conti
     const int* seq_slot;     // [seqs]
 };
 
+struct KidiHeadExtras {      // what a head's result passes beside the plain softmax (each may be null)
+    const float* sinks;      // [heads] float32: exp(sinks[h]) joins head h's softmax denominator
+    const void* gate;        // [rows, ldg] bfloat16: head h of a row is multiplied by sigmoid(gate[row, h])
+    long long ldg;
+};
+
 // `cache` null: every sequence starts at position 0 and its keys are rows of qkv. Else every
 // key and value is read from the cache (64-token pages; no ring), into which the step's own
 // rows have been written already.
 KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int rows, void* out, long long ldo,
                                             const int* seq_len, const int* seq_row0, int seqs, int max_new, int heads,
                                             int kv_heads, int window, float scale, const KidiPromptCache* cache,
-                                            cudaStream_t stream) {
+                                            const KidiHeadExtras* extras, cudaStream_t stream) {
     if (rows <= 0 || seqs <= 0 || max_new <= 0) return 0;
     if (!(scale > 0.f) || heads % kv_heads || (max_new + BM - 1) / BM > 65535 || seqs > 65535 || (ld & 7) ||
         (ldo & 7) || ((uintptr_t)qkv & 15) ||
@@ -716,6 +730,11 @@ KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int r
     p.kv_heads = kv_heads;
     p.window = window;
     p.scale = scale;
+    if (extras) {
+        p.sinks = extras->sinks;
+        p.gate = (const bf16*)extras->gate;
+        p.ldg = extras->ldg;
+    }
     const int group_size = heads / kv_heads;
     dim3 grid(kv_heads * ((group_size + HEADS - 1) / HEADS), seqs, (max_new + BM - 1) / BM);
     attention_prefill_tcgen05_kernel<<<grid, THREADS, SHARED_BYTES, stream>>>(map, k_map, v_map, p);

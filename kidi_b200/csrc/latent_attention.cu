@@ -341,7 +341,7 @@ KIDI_API int kidi_latent_gather(const void* cache, const CacheGeometry* geometry
 
 // ---------------------------------------------------------------------------
 // The folded form on the tensor cores (bfloat16; rank and rot_dim multiples of 16, rank <= 512, pages of 64
-// tokens, no window). A block of eight warps takes one row of the step, a tile of up to 16 of its heads and a share
+// tokens, every page kept; a window is a mask and the first page of the walk). A block of eight warps takes one row of the step, a tile of up to 16 of its heads and a share
 // of its sequence's pages. A page [64 tokens, W = rank + rot_dim] is copied to shared memory once (cp.async) and
 // serves as the keys of S = Q K^T (all W columns) and, its first `rank` columns, as the values of O += P C: the
 // cached rows are read once for all heads of the tile. Warp w of eight computes the scores of the page's tokens
@@ -367,6 +367,7 @@ struct LatentDecodeArgs {
     float scale;
     int splits_are_long;    // > 0: a share holds several pages: worth a second page buffer even at one block an
                             // SM; < 0: one page buffer whatever the sizes
+    int window;             // > 0: a row at position p sees the tokens p - window + 1 .. p only
 };
 
 namespace {
@@ -415,8 +416,9 @@ __global__ void __launch_bounds__(32 * WARPS) latent_decode_kernel(LatentDecodeA
         position = a.row_pos[row];
         slot = a.seq_slot[seq];
         const int pages = (position >> 6) + 1;
-        const int per = (pages + a.splits - 1) / a.splits;
-        first_page = split * per;
+        const int low_page = a.window > 0 ? max(0, position - a.window + 1) >> 6 : 0;   // the first page with a visible token
+        const int per = (pages - low_page + a.splits - 1) / a.splits;
+        first_page = low_page + split * per;
         last_page = min(pages, first_page + per);
     }
     if (first_page >= last_page) {                          // nothing to do: an empty share
@@ -482,7 +484,8 @@ __global__ void __launch_bounds__(32 * WARPS) latent_decode_kernel(LatentDecodeA
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int token = token0 + (e & 1);
-            s[e] = token <= position ? (s[e] + s_other[e]) * a.scale : -INFINITY;
+            const bool seen = token <= position && (a.window <= 0 || token > position - a.window);
+            s[e] = seen ? (s[e] + s_other[e]) * a.scale : -INFINITY;
             top[e >> 1] = fmaxf(top[e >> 1], s[e]);
         }
 #pragma unroll
@@ -499,7 +502,7 @@ __global__ void __launch_bounds__(32 * WARPS) latent_decode_kernel(LatentDecodeA
             float tile = wmax[h];
 #pragma unroll
             for (int w = 1; w < WARPS; ++w) tile = fmaxf(tile, wmax[w * 16 + h]);
-            next[r] = fmaxf(best[r], tile);                 // finite: the page holds a token at or before the position
+            next[r] = fmaxf(best[r], tile);                 // finite: every page of the walk holds a token that the row sees
             keep[r] = expf(best[r] - next[r]);              // 0 on the first page
         }
         {

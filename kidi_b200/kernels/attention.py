@@ -44,7 +44,8 @@ class FastAttentionArgs(ctypes.Structure):
                 ("scale", c_float), ("partial_out", c_void_p), ("partial_stat", c_void_p), ("splits", c_int),
                 ("counters", c_void_p), ("fuse", c_int), ("norm_is_float", c_int), ("q_norm", c_void_p),
                 ("k_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int),
-                ("eps", c_float), ("cache_rows", c_longlong)]
+                ("eps", c_float), ("cache_rows", c_longlong), ("sinks", c_void_p), ("gate", c_void_p),
+                ("ldg", c_longlong)]
 
 
 _libraries: Dict[int, ctypes.CDLL] = {}
@@ -76,7 +77,7 @@ def tensor_memory_library(head_dim: int) -> ctypes.CDLL:
         lib = load_library(f"attention_tcgen05_d{head_dim}", ("attention_tcgen05.cu",), {"KIDI_HEAD_DIM": head_dim})
         lib.kidi_attention_prefill_tcgen05.argtypes = [
             c_void_p, c_longlong, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-            c_float, c_void_p, c_void_p]
+            c_float, c_void_p, c_void_p, c_void_p]
         lib.kidi_attention_prefill_tcgen05.restype = c_int
         lib.kidi_attention_tcgen05_timeout_flag.restype = c_int
         _tensor_memory_libraries[head_dim] = lib
@@ -98,23 +99,40 @@ class PromptCache(ctypes.Structure):
                 ("pages_per_seq", c_int), ("seq_start", c_void_p), ("seq_slot", c_void_p)]
 
 
+class HeadExtras(ctypes.Structure):
+    """A number per head in the softmax denominator and a sigmoid gate per row and head (KidiHeadExtras)."""
+    _fields_ = [("sinks", c_void_p), ("gate", c_void_p), ("ldg", c_longlong)]
+
+
+def extras_fit(sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int) -> bool:
+    """Whether the tensor-core kernels can take these sinks ([heads] float32) and this gate ([rows, heads]
+    bfloat16, unit stride within a row)."""
+    return ((sinks is None or (sinks.dtype == torch.float32 and sinks.is_contiguous() and sinks.numel() == heads))
+            and (gate is None or (gate.dtype == torch.bfloat16 and gate.stride(1) == 1 and gate.shape[1] == heads)))
+
+
 def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.Tensor, seq_row0: torch.Tensor,
                           seqs: int, max_new: int, *, heads: int, kv_heads: int, head_dim: int, scale: float,
                           window: int, kv_view=None, seq_start: Optional[torch.Tensor] = None,
-                          seq_slot: Optional[torch.Tensor] = None) -> None:
+                          seq_slot: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
+                          gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention of packed prompts. Without `kv_view` the prompts start at position 0
     and every key is a row of qkv; with it (a cache of 64-token pages without a ring, into
     which the step's rows have been written) every key and value is read from the cache,
-    so the prompts may continue sequences of `seq_start` tokens."""
+    so the prompts may continue sequences of `seq_start` tokens. `sinks`, `gate`: see `run`."""
     lib = tensor_memory_library(head_dim)
-    cache = None
+    cache = extras = None
+    if sinks is not None or gate is not None:
+        extras = HeadExtras(sinks.data_ptr() if sinks is not None else 0, gate.data_ptr() if gate is not None else 0,
+                            gate.stride(0) if gate is not None else 0)
     if kv_view is not None:
         cache = PromptCache(kv_view.keys.data_ptr(), kv_view.values.data_ptr(), kv_view.keys.numel() // head_dim,
                             kv_view.table.data_ptr(), kv_view.table.shape[1], seq_start.data_ptr(), seq_slot.data_ptr())
     _check(lib.kidi_attention_prefill_tcgen05(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), out.stride(0), seq_len.data_ptr(),
         seq_row0.data_ptr(), seqs, max_new, heads, kv_heads, int(window or 0), float(scale),
-        ctypes.byref(cache) if cache is not None else None, ops._stream()),
+        ctypes.byref(cache) if cache is not None else None, ctypes.byref(extras) if extras is not None else None,
+        ops._stream()),
         "attention_prefill_tcgen05")
 
 
@@ -241,7 +259,7 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     # compute plain scaled scores).
     reshaped = bool(softcap) or slopes is not None
     uneven = value_dim is not None and value_dim != head_dim
-    if (reshaped or uneven or sinks is not None or gate is not None
+    if (reshaped or uneven or not extras_fit(sinks, gate, heads)
             or not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode)
             or (kv_view is not None and kv_view.page_size != 64)):
         ops.attention_generic(qkv, out, heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale,
@@ -249,7 +267,8 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
                               softcap=softcap, slopes=slopes, value_dim=value_dim, sinks=sinks, gate=gate)
         return
     if not decode and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale):
-        common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window)
+        common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window, sinks=sinks,
+                      gate=gate)
         if keys_in_step and int(plan.seq_start.max()) == 0:      # every key is a row of this step
             prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, **common)
             return
@@ -270,6 +289,10 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         tables.row_seq.data_ptr(), tables.row_pos.data_ptr(), tables.seq_slot.data_ptr(), tables.seq_start.data_ptr(),
         tables.seq_len.data_ptr(), tables.seq_row0.data_ptr(), qkv.shape[0], plan.n_seqs, heads, kv_heads,
         int(window or 0), float(scale), 0, 0, 1, 0)
+    if sinks is not None:
+        args.sinks = sinks.data_ptr()
+    if gate is not None:
+        args.gate, args.ldg = gate.data_ptr(), gate.stride(0)
     lib = library(head_dim)
     stream = ops._stream()
     if not decode:

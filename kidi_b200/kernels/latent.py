@@ -154,28 +154,30 @@ class DecodeArgs(ctypes.Structure):
                 ("pages_per_seq", c_int), ("row_seq", c_void_p), ("row_pos", c_void_p), ("seq_slot", c_void_p),
                 ("part_o", c_void_p), ("part_stat", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("rows", c_int),
                 ("heads", c_int), ("rank", c_int), ("rot_dim", c_int), ("splits", c_int), ("scale", c_float),
-                ("splits_are_long", c_int)]
+                ("splits_are_long", c_int), ("window", c_int)]
 
 
 def tensor_core_fits(dtype: torch.dtype, rank: int, rot_dim: int, window, kv_view) -> bool:
     """Whether the folded form can run on the tensor cores: bfloat16, widths in multiples of 16, a latent of at
-    most 512 values, a cache of 64-token pages that keeps every page."""
-    return (dtype == torch.bfloat16 and rank % 16 == 0 and rot_dim % 16 == 0 and 0 < rank <= 512 and window is None
+    most 512 values, a cache of 64-token pages that keeps every page (a window is then a mask)."""
+    return (dtype == torch.bfloat16 and rank % 16 == 0 and rot_dim % 16 == 0 and 0 < rank <= 512
             and (kv_view is None or (kv_view.page_size == 64 and kv_view.ring_pages == 0
                                      and kv_view.keys.is_contiguous() and kv_view.table.is_contiguous())))
 
 
-def decode_splits(rows: int, heads: int, longest: int, device: torch.device) -> int:
+def decode_splits(rows: int, heads: int, longest: int, device: torch.device, window=None) -> int:
     """How many blocks share a sequence's pages: as many as fill the GPU once (every share costs a trip of its
-    partial result through the workspace), at most one a page."""
+    partial result through the workspace), at most one a page (of those a window reaches)."""
     from .attention import sm_count
     pages = max(1, -(-longest // 64))
+    if window:
+        pages = min(pages, (int(window) + 62) // 64 + 1)
     tiles = -(-heads // 16)
     return max(1, min(pages, sm_count(device) // max(1, rows * tiles)))
 
 
 def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads: int, rank: int, rot_dim: int,
-                          scale: float, kv_view, splits: Optional[int] = None) -> None:
+                          scale: float, kv_view, splits: Optional[int] = None, window=None) -> None:
     """The folded form on the tensor cores (see `attention`), every row of the step against its sequence's pages;
     the shares of a row's pages meet in a workspace and a second kernel merges them."""
     ops._need_cuda(folded, out)
@@ -184,7 +186,10 @@ def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads
             or out.stride(1) != 1 or folded.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 \
             or kv_view.keys.shape[-1] != rank + rot_dim:
         raise invalid_argument("latent attention: folded queries, output or cache have the wrong shape")
-    splits = splits or decode_splits(rows, heads, ctx.plan.max_total, folded.device)
+    splits = splits or decode_splits(rows, heads, ctx.plan.max_total, folded.device, window)
+    reach = -(-ctx.plan.max_total // 64)
+    if window:
+        reach = min(reach, (int(window) + 62) // 64 + 1)
     count = int(library().kidi_latent_decode_workspace(rows, heads, rank, splits))
     workspace = ctx.workspace("latent_partial", count)
     tables = ctx.tables
@@ -193,5 +198,5 @@ def attention_tensor_core(ctx, folded: torch.Tensor, out: torch.Tensor, *, heads
                       tables.seq_slot.data_ptr(), workspace.data_ptr(),
                       workspace.data_ptr() + rows * splits * heads * rank * 4, out.data_ptr(), out.stride(0), rows,
                       heads, rank, rot_dim, splits, float(scale),
-                      -1 if PAGE_BUFFERS == 1 else 1 if PAGE_BUFFERS == 2 or -(-ctx.plan.max_total // 64) > splits else 0)
+                      -1 if PAGE_BUFFERS == 1 else 1 if PAGE_BUFFERS == 2 or reach > splits else 0, int(window or 0))
     _check(library().kidi_latent_decode(ctypes.byref(args), ops._stream()), f"latent_attention[mma.sync, {splits} shares]", 2)

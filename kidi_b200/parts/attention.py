@@ -173,7 +173,7 @@ class Attention(Part):
             raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
         # One token per sequence on the tensor-core path: the attention kernel takes the rows as
         # the projection left them and does norm, rotation and the cache write itself.
-        fused = owns_cache and store_first and not extras and self.launcher.fuses_rotation(
+        fused = owns_cache and store_first and self.value_dim == self.head_dim and self.launcher.fuses_rotation(
             plan, qkv, kv_view=view, q_norm=self.q_norm, k_norm=self.k_norm, **rotate)
         if not fused:
             ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,

@@ -193,7 +193,7 @@ class LatentAttention(Part):
         widths the tensor-core prompt kernels take."""
         plan, width = ctx.plan, self.dim + self.rot_dim
         return (x.dtype == torch.bfloat16 and not plan.is_decode and int(plan.seq_start.max()) == 0
-                and self.vdim <= width and self.window is None
+                and self.vdim <= width
                 and attention_kernels.fast_fits(x.dtype, self.heads, self.heads, width, False)
                 and (view is None or view.page_size == 64))
 
@@ -205,9 +205,10 @@ class LatentAttention(Part):
     def launch_signature(self, rows: int, longest: int) -> tuple:
         """What a captured decode step freezes: into how many shares the tensor-core kernel cuts a sequence's
         pages (the general kernel, which the 32-bit engine runs, has no such choice)."""
-        if not latent_kernels.tensor_core_fits(self.env.dtype, self.rank, self.rot_dim, self.window, None):
+        if (self.window is not None and self.ring) or not latent_kernels.tensor_core_fits(
+                self.env.dtype, self.rank, self.rot_dim, self.window, None):
             return ()
-        return (latent_kernels.decode_splits(rows, self.heads, longest, self.env.device),)
+        return (latent_kernels.decode_splits(rows, self.heads, longest, self.env.device, self.window),)
 
     def forward(self, x, ctx, views, owns_cache: bool, sink=None) -> Optional[torch.Tensor]:
         x = plain_rows(x)
@@ -234,7 +235,7 @@ class LatentAttention(Part):
         summed = torch.empty((rows, heads * rank), dtype=q.dtype, device=q.device)
         if latent_kernels.tensor_core_fits(q.dtype, rank, rot_dim, self.window, view):
             latent_kernels.attention_tensor_core(ctx, folded, summed, heads=heads, rank=rank, rot_dim=rot_dim,
-                                                 scale=self.scale, kv_view=view)
+                                                 scale=self.scale, kv_view=view, window=self.window)
         else:
             latent_kernels.attention(folded, summed, heads=heads, rank=rank, rot_dim=rot_dim, scale=self.scale,
                                      window=self.window, tables=ctx.tables, kv_view=view)
@@ -260,7 +261,5 @@ class LatentAttention(Part):
                                      vdim=self.vdim, tables=ctx.tables, **rotation)
         attended = torch.empty((rows, heads * width), dtype=q.dtype, device=q.device)
         attention_kernels.run(ctx, packed, attended, heads=heads, kv_heads=heads, head_dim=width, scale=self.scale,
-                              window=None, kv_view=None, keys_in_step=True)
-        if gate is not None:
-            ops.head_gate(attended, gate, heads, width)
+                              window=self.window, kv_view=None, keys_in_step=True, gate=gate)
         return out.forward(attended)
