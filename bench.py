@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--model 8b|14b|32b] [--impl ours|reference]
-    python bench.py --design sanozen|gakenex [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
+    python bench.py --design sanozen|gakenex|gazezen [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
 
 A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
 layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
@@ -327,7 +327,30 @@ def gakenex_shape(width: int, layers: int = 4) -> dict:
             "logit_softcap": 30.0, "layers": stack}
 
 
-DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape}
+def gazezen_shape(width: int, layers: int = 4) -> dict:
+    """A Gazezen stack at the layer sizes of a model of `width`: attention layers (heads of 128, a key/value head
+    for four heads, half of a head rotated, a window of 4,096, sinks and head gates) in turn with latent
+    attention layers (64 plain + 64 rotated query/key dimensions, values of 128, a latent of width / 8, stretched
+    frequencies, the same window and gates); every layer's feed-forward routes over 16 plain gelu experts in four
+    groups of which two are kept, two experts a token plus a shared one, each of half the Qwen3 layers'
+    feed-forward size (a token uses as many feed-forward weights). No range of layers is run twice, so that both
+    stacks run as many layers."""
+    heads = width // 128
+    inter = (8 * width // 3 + 127) // 128 * 128
+    mlp = {"kind": "moe", "expert": {"ff": inter // 2}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}},
+           "shared": {"ff": inter // 2}}
+    attention = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": 4096}, "rot": {"base": 10000.0, "dims": 64}}
+    latent = {"heads": heads, "dim": 64, "rot_dim": 64, "vdim": 128, "kv_rank": width // 8, "scale": 128 ** -0.5,
+              "mask": {"size": 4096}, "rot": {"base": 10000.0, "dims": 64, "scaling": {
+                  "factor": 8.0, "original": 1024.0, "fast": 32.0, "slow": 1.0}}}
+    stack = [{"type": "attention" if index % 2 == 0 else "latent_attention",
+              "mixer": dict(attention if index % 2 == 0 else latent), "mlp": dict(mlp)} for index in range(layers)]
+    return {"architecture": "Gazezen", "vocab": 32768, "width": width, "max_positions": 8192, "norm": {"eps": 1e-5},
+            "logit_scale": 0.5, "layers": stack}
+
+
+DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape, "gazezen": gazezen_shape}
 
 
 def qwen3_shape(width: int, layers: int = 4) -> dict:
@@ -345,7 +368,7 @@ KERNEL_CLASSES = (
     ("decode attention", ("attention_decode", "latent_attention")),
     ("recurrence", ("gated_recurrence",)),
     ("stream norm", ("add_rmsnorm", "add_layernorm")),
-    ("activation", ("silu_gate", "poly_norm", "bounded_gate")),
+    ("activation", ("silu_gate", "poly_norm", "bounded_gate", "gelu")),
     ("experts through the choice", ("expert_slots",)),
 )
 
@@ -414,6 +437,38 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
         work["decode attention"] = ("bytes", cache)
         if decode:
             work["experts through the choice"] = ("bytes", chosen)
+    elif design == "gazezen":
+        width, layers = config["width"], config["layers"]
+        weights, norms, act_width, attention, cache, chosen = config["vocab"] * width, 1, 0, 0.0, 0.0, 0.0
+        for layer in layers:
+            m, mlp = layer["mixer"], layer["mlp"]
+            heads, vdim = m["heads"], m["vdim"]
+            norms += 4 if mlp else 2
+            if layer["type"] == "attention":
+                groups, dim = m["kv_heads"], m["dim"]
+                weights += width * (heads * dim + groups * (dim + vdim) + heads) + heads * vdim * width
+                attention += 2.0 * heads * (dim + vdim) * rows * (rows + 1) / 2
+                cache += rows * min(context, m["mask"]["size"]) * groups * (dim + vdim) * 2.0
+            else:
+                head, rank = m["dim"] + m["rot_dim"], m["kv_rank"]
+                weights += width * (heads * head + rank + m["rot_dim"] + heads) + heads * (m["dim"] + vdim) * rank \
+                    + heads * vdim * width
+                attention += 4.0 * heads * head * rows * (rows + 1) / 2             # values padded to the key width
+                cache += rows * min(context, m["mask"]["size"]) * (rank + m["rot_dim"]) * 2.0
+            if mlp:
+                router, ff, shared = mlp["router"], mlp["expert"]["ff"], (mlp.get("shared") or {}).get("ff", 0)
+                weights += router["experts"] * width + 2 * width * shared
+                used = 2 * width * ff * router["top"]                                # per token
+                act_width += 2 * shared
+                if decode:     # each (row, choice) streams its expert's weights (rows * top <= experts here)
+                    chosen += rows * used * 2.0
+                else:
+                    weights += used
+                    act_width += 2 * ff * router["top"]
+        work["prompt attention"] = ("flops", attention)
+        work["decode attention"] = ("bytes", cache)
+        if decode:
+            work["experts through the choice"] = ("bytes", chosen)
     else:
         width, layers = config["width"], config["layers"]
         weights, norms, act_width, attention, cache, scan_flops, scan_bytes, state = config["vocab"] * width, 1, 0, 0.0, 0.0, 0.0, 0.0, 0.0
@@ -447,7 +502,7 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
 
 
 def design_comparison(args) -> int:
-    """`--design sanozen` / `--design gakenex`: prompts and decoding of a stack of that design beside Qwen3 layers
+    """`--design sanozen` / `--design gakenex` / `--design gazezen`: prompts and decoding of a stack of that design beside Qwen3 layers
     of equal size, with every class of kernel against its roofline."""
     import torch
     from kidi_b200 import Engine
@@ -509,8 +564,8 @@ def design_comparison(args) -> int:
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--design", default="", choices=["", "sanozen", "gakenex"],
-                        help="a Sanozen or Gakenex stack beside Qwen3 layers of equal size, kernel class by kernel class "
+    parser.add_argument("--design", default="", choices=["", "sanozen", "gakenex", "gazezen"],
+                        help="a Sanozen, Gakenex or Gazezen stack beside Qwen3 layers of equal size, kernel class by kernel class "
                              "(the default workload is left as it is)")
     parser.add_argument("--widths", default="2048,4096", help="model widths of --design runs")
     parser.add_argument("--gpus", type=int, default=1)

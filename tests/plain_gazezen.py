@@ -145,12 +145,22 @@ def choose(scores: torch.Tensor, top: int, groups: Optional[Mapping]) -> torch.T
     return torch.topk(allowed, top).indices
 
 
-def routed_feed_forward(h: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str, mlp: Mapping) -> torch.Tensor:
+def routed_feed_forward(h: torch.Tensor, w: Mapping[str, torch.Tensor], prefix: str, mlp: Mapping,
+                        given: Optional[torch.Tensor] = None, margin: float = 0.0) -> torch.Tensor:
+    """`given` [T, top]: another implementation's choices. A token takes them instead of its own only if they are
+    its own choice once the given experts' scores are raised and the others' lowered by the factor `margin` (a
+    close call that fell the other way); the weights are always this function's own scores."""
     router = mlp["router"]
+    top, groups = int(router["top"]), router.get("groups")
     scores = torch.softmax(lin(w[prefix + "router"], h), -1)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
-        chosen = choose(scores[t], int(router["top"]), router.get("groups"))
+        chosen = choose(scores[t], top, groups)
+        if given is not None and sorted(given[t].tolist()) != sorted(chosen.tolist()):
+            tilted = scores[t] * (1.0 - margin)
+            tilted[given[t].long()] = scores[t, given[t].long()] * (1.0 + margin)
+            if sorted(choose(tilted, top, groups).tolist()) == sorted(given[t].tolist()):
+                chosen = given[t].long()
         total = scores[t, chosen].sum() + 1e-20
         for index in chosen.tolist():
             out[t] += scores[t, index] / total * expert(h[t:t + 1], w, f"{prefix}e{index}.")[0]
@@ -174,11 +184,15 @@ def run_order(config: Mapping) -> List[tuple]:
 
 
 def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens, dtype=torch.float64,
-            streams: Optional[List[torch.Tensor]] = None) -> torch.Tensor:
+            streams: Optional[List[torch.Tensor]] = None, choices: Optional[List[torch.Tensor]] = None,
+            margin: float = 0.0) -> torch.Tensor:
+    """`choices`: for every run of a layer with a feed-forward, in the order they run, the experts [T, top] that
+    another implementation chose (see `routed_feed_forward`)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     w = {name: (tensor.to(dtype) if tensor.is_floating_point() else tensor) for name, tensor in w.items()}
     eps = float(config["norm"]["eps"])
     x = w["embed"][tokens]
+    routed_runs = 0
     for index, step in run_order(config):
         layer, prefix = config["layers"][index], f"l{index}."
         if step is not None:
@@ -191,7 +205,10 @@ def forward(config: Mapping, w: Mapping[str, torch.Tensor], tokens, dtype=torch.
         x = x + centred_norm(mixed, w[prefix + "norm1b"], eps)
         if layer.get("mlp") is not None:
             h = centred_norm(x, w[prefix + "norm2"], eps)
-            x = x + centred_norm(routed_feed_forward(h, w, prefix + "mlp.", layer["mlp"]), w[prefix + "norm2b"], eps)
+            given = choices[routed_runs] if choices is not None else None
+            routed_runs += 1
+            x = x + centred_norm(routed_feed_forward(h, w, prefix + "mlp.", layer["mlp"], given, margin),
+                                 w[prefix + "norm2b"], eps)
         if streams is not None:
             streams.append(x.clone())
     return lin(w["head"], centred_norm(x, w["final.norm"], eps)) * float(config.get("logit_scale", 1.0))
