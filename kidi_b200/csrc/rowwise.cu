@@ -97,6 +97,21 @@ __global__ void gelu_kernel(const T* __restrict__ z, T* __restrict__ out, long l
     out[at] = from_float<T>(0.5f * v * (1.0f + erff(v * 0.70710678118654752440f)));
 }
 
+// The same for bfloat16, eight elements (16 bytes) a thread; `groups` = total / 8.
+__global__ void gelu_bf16x8_kernel(const bf16* __restrict__ z, bf16* __restrict__ out, long long groups) {
+    const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (at >= groups) return;
+    uint4 raw = *reinterpret_cast<const uint4*>(z + at * 8);
+    __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 v = __bfloat1622float2(pairs[k]);
+        pairs[k] = __floats2bfloat162_rn(0.5f * v.x * (1.0f + erff(v.x * 0.70710678118654752440f)),
+                                         0.5f * v.y * (1.0f + erff(v.y * 0.70710678118654752440f)));
+    }
+    *reinterpret_cast<uint4*>(out + at * 8) = raw;
+}
+
 // x *= factor, element by element (x 32-bit, in place).
 __global__ void scale_kernel(float* __restrict__ x, long long total, float factor) {
     const long long at = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -317,6 +332,9 @@ KIDI_API int kidi_gelu(const void* z, void* out, int dtype, long long total, cud
     if (total <= 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == KIDI_F32) return kidi_launch(gelu_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, total);
+    if (dtype == KIDI_BF16 && !(total & 7) && !((uintptr_t)z & 15) && !((uintptr_t)out & 15))
+        return kidi_launch(gelu_bf16x8_kernel, (unsigned)(((total >> 3) + 255) / 256), 256, 0, stream, (const bf16*)z,
+                           (bf16*)out, total >> 3);
     if (dtype == KIDI_BF16) return kidi_launch(gelu_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)z, (bf16*)out, total);
     return KIDI_REFUSED_DTYPE;
 }

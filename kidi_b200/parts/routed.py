@@ -22,10 +22,10 @@ result is added with weight 1.
 
 Steps of few rows, steps inside a captured decode graph, and every step of the 32-bit engine read the
 chosen experts' weights through the choice on the device (no host round trip). Prompts of the bfloat16
-engine sort the (row, choice) pairs by expert on the host and gather the scaled rows; every expert's rows are
-then padded to one count and run through two batched products of the vendor library, or, where one expert has
-far more rows than the others or the widths are no multiples of 8, each expert's rows through the ordinary
-products.
+engine sort the (row, choice) pairs by expert on the host and gather the rows; every expert's rows, up to twice
+the mean count, are then padded to one count and run through two batched products of the vendor library, and
+what an expert has beyond that (or everything, where the widths are no multiples of 8) through the ordinary
+products, with one activation kernel for all of them.
 """
 from __future__ import annotations
 
@@ -148,34 +148,44 @@ class RoutedExperts(Part):
         picked = chosen.reshape(-1).cpu().numpy()
         order = np.argsort(picked, kind="stable").astype(np.int32)
         counts = np.bincount(picked, minlength=self.experts)
+        # Every expert's first `cap` rows stand in one padded batch [experts, cap] (two batched products of the
+        # vendor library for all experts); the rows that an expert has beyond `cap` follow the batch, expert by
+        # expert, and run through the ordinary products. `cap` is the largest count, but at most twice the mean, so
+        # that the padding stays below the rows themselves however uneven the choice is. Widths that are no
+        # multiples of 8 take the ordinary products only (cap 0).
+        cap = 0
+        if self.hidden % 8 == 0 and self.inter % 8 == 0:
+            cap = int(-(-min(int(counts.max()), -(-2 * slots // self.experts)) // 8) * 8)
+        begins = np.concatenate([[0], np.cumsum(counts)[:-1]])
+        experts_sorted = picked[order]
+        within = np.arange(slots) - begins[experts_sorted]
+        over = within >= cap
+        extra = np.maximum(counts - cap, 0)
+        extra_begins = self.experts * cap + np.concatenate([[0], np.cumsum(extra)[:-1]])
+        at = np.where(over, extra_begins[experts_sorted] + within - cap, experts_sorted * cap + within).astype(np.int32)
+        total = self.experts * cap + int(extra.sum())
+        source = np.full(total, -1, dtype=np.int32)
+        source[at] = order
         place = np.empty(slots, dtype=np.int32)
-        most = int(-(-int(counts.max()) // 8) * 8)
-        if self.hidden % 8 == 0 and self.inter % 8 == 0 and self.experts * most <= 3 * slots:
-            # Every expert's rows padded to one count: two batched products of the vendor library and one gate
-            # for all experts (taken unless one expert has far more rows than the others).
-            begins = np.concatenate([[0], np.cumsum(counts)[:-1]])
-            experts_sorted = picked[order]
-            at = (experts_sorted * most + (np.arange(slots) - begins[experts_sorted])).astype(np.int32)
-            padded = np.full(self.experts * most, -1, dtype=np.int32)
-            padded[at] = order
-            place[order] = at
-            both_tables = torch.from_numpy(np.concatenate([padded, place])).to(x.device)
-            gathered = routed.gather_slots(x, both_tables[:padded.size], weight, self.top, self.weight_on_input)
-            both = torch.bmm(gathered.view(self.experts, most, self.hidden), self.gate_up.transpose(1, 2))
+        place[order] = at
+        tables = torch.from_numpy(np.concatenate([source, place])).to(x.device)
+        gathered = routed.gather_slots(x, tables[:total], weight, self.top, self.weight_on_input)
+        first = torch.empty((total, self.gate_up.shape[1]), dtype=x.dtype, device=x.device)
+        result = torch.empty((total, self.hidden), dtype=x.dtype, device=x.device)
+        batch = self.experts * cap
+        spans = [(index, int(begin), int(begin + count)) for index, (begin, count) in enumerate(zip(extra_begins, extra))
+                 if count]
+        if cap:
+            torch.bmm(gathered[:batch].view(self.experts, cap, self.hidden), self.gate_up.transpose(1, 2),
+                      out=first[:batch].view(self.experts, cap, first.shape[1]))
             ops.note("library_bmm")
-            mid = self._activate(both.view(self.experts * most, both.shape[-1]))
-            result = torch.bmm(mid.view(self.experts, most, self.inter), self.down.transpose(1, 2))
+        for index, begin, end in spans:
+            self._gate_up[index].forward(gathered[begin:end], out=first[begin:end])
+        mid = self._activate(first)                  # one activation kernel for the rows of all experts
+        if cap:
+            torch.bmm(mid[:batch].view(self.experts, cap, self.inter), self.down.transpose(1, 2),
+                      out=result[:batch].view(self.experts, cap, self.hidden))
             ops.note("library_bmm")
-            return routed.combine_slots(result.view(self.experts * most, self.hidden), both_tables[padded.size:], weight,
-                                        rows, self.top, self.weight_on_input, addend)
-        place[order] = np.arange(slots, dtype=np.int32)
-        both = torch.from_numpy(np.concatenate([order, place])).to(x.device)
-        gathered = routed.gather_slots(x, both[:slots], weight, self.top, self.weight_on_input)
-        result = torch.empty((slots, self.hidden), dtype=x.dtype, device=x.device)
-        begin = 0
-        for index, count in enumerate(counts.tolist()):
-            if count:
-                mid = self._activate(self._gate_up[index].forward(gathered[begin:begin + count]))
-                self._down[index].forward(mid, out=result[begin:begin + count])
-                begin += count
-        return routed.combine_slots(result, both[slots:], weight, rows, self.top, self.weight_on_input, addend)
+        for index, begin, end in spans:
+            self._down[index].forward(mid[begin:end], out=result[begin:end])
+        return routed.combine_slots(result, tables[total:], weight, rows, self.top, self.weight_on_input, addend)
