@@ -153,9 +153,11 @@ def test_the_router_alone(experts, top, groups, keep):
 @pytest.mark.parametrize("experts,top,groups,keep,rows,inter,shared", [
     (6, 2, 3, 2, 5, 24, 40), (4, 4, 1, 1, 300, 24, None), (16, 2, 4, 1, 200, 24, 8), (8, 3, 4, 3, 64, 40, 24),
     (4, 2, 2, 1, 150, 20, 36), (16, 2, 4, 2, 700, 64, 64)])
-def test_routed_experts_alone(dtype, experts, top, groups, keep, rows, inter, shared):
+@pytest.mark.parametrize("lopsided", [False, True])
+def test_routed_experts_alone(dtype, experts, top, groups, keep, rows, inter, shared, lopsided):
     """The feed-forward part alone (router, plain gelu experts weighted on their results, the shared expert added)
-    on few rows and many, decoding and prompts, against the plain function."""
+    on few rows and many, decoding and prompts, against the plain function. `lopsided`: every row chooses expert 0
+    among its experts, so that one expert has several times the mean count of rows."""
     from types import SimpleNamespace
     from kidi_b200.parts.base import BuildEnv
     from kidi_b200.parts.routed import RoutedExperts
@@ -168,8 +170,12 @@ def test_routed_experts_alone(dtype, experts, top, groups, keep, rows, inter, sh
         ff = shared if name == "shared" else inter
         w[f"m.{name}.up"] = torch.randn(ff, hidden, generator=generator) * 0.3
         w[f"m.{name}.down"] = torch.randn(hidden, ff, generator=generator) * 0.3
+    h = torch.randn(rows, hidden, generator=generator)
+    if lopsided:
+        w["m.router"][0, 0] = 2.0
+        h[:, 0] += 4.0
     w = {name: tensor.to(dtype) for name, tensor in w.items()}
-    h = torch.randn(rows, hidden, generator=generator).to(dtype)
+    h = h.to(dtype)
     mlp = {"router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}},
            "shared": {"ff": shared} if shared else None}
     want = plain_gazezen.routed_feed_forward(h.double(), {n: t.double() for n, t in w.items()}, "m.", mlp)
