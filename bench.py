@@ -347,7 +347,7 @@ def gazezen_shape(width: int, layers: int = 4) -> dict:
     stack = [{"type": "attention" if index % 2 == 0 else "latent_attention",
               "mixer": dict(attention if index % 2 == 0 else latent), "mlp": dict(mlp)} for index in range(layers)]
     return {"architecture": "Gazezen", "vocab": 32768, "width": width, "max_positions": 8192, "norm": {"eps": 1e-5},
-            "logit_scale": 0.5, "layers": stack}
+            "logit_scale": 0.7, "layers": stack}
 
 
 DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape, "gazezen": gazezen_shape}

@@ -124,7 +124,7 @@ def test_the_small_kernels(dtype):
         assert torch.allclose(got.double().cpu(), want, atol=2e-5 if dtype == torch.float32 else 4e-2)
 
 
-@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (8, 4, 2, 1), (12, 3, 4, 2), (16, 2, 4, 1), (5, 5, 1, 1),
+@pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (10, 4, 2, 1), (12, 3, 4, 2), (16, 2, 4, 1), (5, 5, 1, 1),
                                                      (9, 1, 3, 3), (64, 6, 8, 3)])
 def test_the_router_alone(experts, top, groups, keep):
     """Softmax over all experts, the best groups kept, the largest scores among them, divided by their sum: the
