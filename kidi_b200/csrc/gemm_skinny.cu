@@ -48,6 +48,7 @@ struct Epilogue {
     long long ld_normed;
     float* parts_out;
     int parts_stride;
+    int gelu;                     // the plain store writes gelu(y + bias), the exact (erf) form, instead of y + bias
 };
 
 __device__ __forceinline__ uint4 load_streaming(const void* pointer) {
@@ -245,6 +246,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
             for (int offset = span / 2; offset > 0; offset >>= 1) square += __shfl_xor_sync(0xffffffffu, square, offset);
             if (r == 0 && m < M) e.parts_out[(long long)m * e.parts_stride + blockIdx.x] = square;
         } else if (inside) {
+            if (!GATED && e.gelu) sum = 0.5f * sum * (1.0f + erff(sum * 0.70710678118654752440f));
             y[m * ldy + n0 + r] = from_float<TY>(sum);
         }
     }
@@ -293,6 +295,7 @@ struct KidiSkinnyExtras {          // every pointer may be null: the plain produ
     long long ld_normed;
     float* parts_out;
     int parts_stride;
+    int gelu;                      // not gated, not into the residual: the result passes the exact gelu
 };
 
 // How many parts per row the product into the residual writes for N features.
@@ -320,6 +323,8 @@ KIDI_API int kidi_gemm_skinny(const void* x, const void* w, void* y, int y_dtype
         e.ld_normed = extras->ld_normed;
         e.parts_out = extras->parts_out;
         e.parts_stride = extras->parts_stride;
+        e.gelu = extras->gelu;
+        if (e.gelu && (gated || e.residual)) return KIDI_REFUSED_SIZE;
         if (e.factor_parts && (e.factor_count < 1 || e.factor_stride < e.factor_count || e.factor_width < 1))
             return KIDI_REFUSED_SIZE;
         if (e.residual && (gated || !e.norm_weight || !e.normed || !e.parts_out || e.parts_stride < (N + 15) / 16))

@@ -23,7 +23,7 @@ class Extras(ctypes.Structure):
     _fields_ = [("factor_parts", c_void_p), ("factor_count", c_int), ("factor_stride", c_int),
                 ("factor_width", c_int), ("factor_eps", c_float), ("residual", c_void_p), ("ld_residual", c_longlong),
                 ("norm_weight", c_void_p), ("norm_weight_is_float", c_int), ("normed", c_void_p),
-                ("ld_normed", c_longlong), ("parts_out", c_void_p), ("parts_stride", c_int)]
+                ("ld_normed", c_longlong), ("parts_out", c_void_p), ("parts_stride", c_int), ("gelu", c_int)]
 
 
 _bound = False
@@ -78,10 +78,12 @@ def _factor_fields(extras: Extras, factors) -> None:
 
 
 def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None,
-         row_tiles: Optional[int] = None, bias: Optional[torch.Tensor] = None, factors=None) -> torch.Tensor:
+         row_tiles: Optional[int] = None, bias: Optional[torch.Tensor] = None, factors=None,
+         activation: Optional[str] = None) -> torch.Tensor:
     """y = x @ weight.T (+ bias, float32) for x [M <= 64, K], weight [N, K], both bfloat16. With
     `factors` = (parts, width, eps) every row m of the result is multiplied by
-    1 / sqrt(sum(parts[m]) / width + eps) first (the factor that an RMSNorm left out of x)."""
+    1 / sqrt(sum(parts[m]) / width + eps) first (the factor that an RMSNorm left out of x).
+    `activation` "gelu": the result passes the exact (erf) gelu in the epilogue, in 32-bit."""
     _need_cuda(x, weight, bias)
     ops.check_bias(bias, weight.shape[0])
     if not supports(x, weight) or x.shape[1] != weight.shape[1]:
@@ -90,12 +92,15 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
     N = weight.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if activation not in (None, "gelu"):
+        raise invalid_argument("gemm_skinny: the epilogue knows the activation 'gelu' only")
     extras = Extras()
     _factor_fields(extras, factors)
+    extras.gelu = int(activation == "gelu")
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
                                        weight.stride(0), out.stride(0), 0, row_tiles or _row_tiles(N, M, x.device), _ptr(bias),
                                        ctypes.byref(extras), _stream()),
-           "gemm_skinny[row factors]" if factors is not None else "gemm_skinny")
+           "gemm_gelu[skinny]" if activation else "gemm_skinny[row factors]" if factors is not None else "gemm_skinny")
     return out
 
 

@@ -35,7 +35,7 @@ import numpy as np
 import torch
 
 from ..errors import invalid_argument, unsupported
-from ..kernels import ops, routed
+from ..kernels import ops, routed, skinny
 from .base import Part, plain_rows
 from .linear import Linear
 from .registry import register_part
@@ -132,7 +132,11 @@ class RoutedExperts(Part):
         if self._shared is not None:
             # The shared expert's result joins the routed sum in the kernel that forms it (a 32-bit sum).
             up, down = self._shared
-            shared = down.forward(self._activate(up.forward(x)))
+            if not self.gated and up.bias is None and skinny.fits(x, up.weight):
+                mid = skinny.gemm(x, up.weight, x.dtype, activation="gelu")       # few rows: the gelu in the epilogue
+            else:
+                mid = self._activate(up.forward(x))
+            shared = down.forward(mid)
         return self._forward_routed(x, ctx, shared)
 
     def _forward_routed(self, x, ctx, addend=None) -> torch.Tensor:

@@ -124,6 +124,19 @@ def test_the_small_kernels(dtype):
         assert torch.allclose(got.double().cpu(), want, atol=2e-5 if dtype == torch.float32 else 4e-2)
 
 
+def test_the_gelu_behind_a_product_of_few_rows():
+    """The weight-streaming product with the exact gelu in its epilogue against gelu(x W^T), 1 to 64 rows."""
+    from kidi_b200.kernels import skinny
+    generator = torch.Generator().manual_seed(5)
+    for rows, features, inner in ((1, 40, 64), (8, 96, 72), (33, 200, 256), (64, 24, 128)):
+        x = torch.randn(rows, inner, generator=generator).to(torch.bfloat16).cuda()
+        w = (torch.randn(features, inner, generator=generator) * 2 / inner ** 0.5).to(torch.bfloat16).cuda()
+        want = plain_gazezen.gelu_erf(x.double().cpu() @ w.double().cpu().t())
+        got = skinny.gemm(x, w, torch.bfloat16, activation="gelu").double().cpu()
+        assert torch.allclose(got, want, atol=2e-2, rtol=1e-2), (rows, features, inner)
+        assert float((got - want).abs().mean()) < 3e-3
+
+
 @pytest.mark.parametrize("experts,top,groups,keep", [(6, 2, 3, 2), (10, 4, 2, 1), (12, 3, 4, 2), (16, 2, 4, 1), (5, 5, 1, 1),
                                                      (9, 1, 3, 3), (64, 6, 8, 3)])
 def test_the_router_alone(experts, top, groups, keep):
