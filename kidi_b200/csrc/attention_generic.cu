@@ -36,6 +36,8 @@ struct RopeStoreArgs {
     float eps;
     int transform;             // 0: only copy the k and v heads, as they are, to the cache
     int value_dim;             // width of a v head (0: head_dim); the v heads follow the k heads in a row
+    const float* q_scale;      // [positions] or null: a q head at position p is multiplied by q_scale[p] (after the
+                               // norm and the rotation)
 };
 
 // One warp per (row, head) over heads + 2*kv_heads heads.
@@ -113,6 +115,7 @@ __global__ void __launch_bounds__(128) rope_store_kernel(RopeStoreArgs a) {
             const float rotated = c < half ? -normed[warp][c + half] : normed[warp][c - half];
             out = values[i] * cosine + rotated * sine;
         }
+        if (a.q_scale && head < a.heads) out *= a.q_scale[position];
         const T stored = from_float<T>(out);
         vector[c] = stored;
         if (cached) cached[c] = stored;
@@ -221,6 +224,11 @@ __global__ void __launch_bounds__(128) rope_store_bf16_kernel(RopeStoreArgs a, i
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[i] = v[i] * c8[i] + (low ? -other[i] : other[i]) * s8[i];
         }
+    }
+    if (mine && !plain && a.q_scale && head < a.heads) {
+        const float factor = a.q_scale[position];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= factor;
     }
     if (mine && !plain) {
         uint4 packed;

@@ -654,6 +654,7 @@ struct KidiPromptCache {     // where the keys and values lie when prompts conti
     int pages_per_seq;
     const int* seq_start;    // [seqs]
     const int* seq_slot;     // [seqs]
+    int q_only;              // the rows of qkv hold the query heads only (the layer reads another layer's cache)
 };
 
 struct KidiHeadExtras {      // what a head's result passes beside the plain softmax (each may be null)
@@ -677,7 +678,7 @@ KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int r
     EncodeTiled encode = encode_tiled();
     if (!encode) return KIDI_REFUSED_SIZE;
     CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)(heads + 2 * kv_heads) * D, (cuuint64_t)rows};
+    const cuuint64_t dims[2] = {(cuuint64_t)(cache && cache->q_only ? heads : heads + 2 * kv_heads) * D, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
     const cuuint32_t box[2] = {64, 128};
     const cuuint32_t steps[2] = {1, 1};

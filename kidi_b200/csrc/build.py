@@ -40,12 +40,13 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr", "-
 # The libraries of the package: name -> sources. Definitions are added per request.
 LIBRARIES: Dict[str, Tuple[str, ...]] = {
     "core": ("elementwise.cu", "rowwise.cu", "gemm_simt.cu", "gemm_skinny.cu", "gemm_tcgen05.cu",
-             "attention_generic.cu", "sampling.cu"),
+             "attention_generic.cu", "sampling.cu", "lanes.cu"),
     # mixers that only some architectures have: built when a model with such a layer first runs
     "latent_attention": ("latent_attention.cu",),
     "gated_recurrence": ("gated_recurrence.cu",),
     "differential_attention": ("differential_attention.cu",),
     "routed": ("routed.cu",),
+    "scalar_recurrence": ("scalar_recurrence.cu",),
 }
 
 _loaded: Dict[str, ctypes.CDLL] = {}

@@ -1,0 +1,242 @@
+// A residual stream kept as several lanes (copies that layers read as one weighted sum and write back
+// through a small mixing matrix), and a few row-wise kernels of mixers that run side by side.
+//
+//   lanes_rmsnorm:    u = sum_s read[s] * lane_s (read absent: the plain sum);  y = u / sqrt(mean(u^2) + eps) * w
+//   lanes_mix:        lane'_t = sum_s mix[s, t] * lane_s + write[t] * y          (all lanes at once, from the old ones)
+//   normed_pair_sum:  z = ca * a / rms(a) * wa + cb * b / rms(b) * wb
+//   sigmoid_gate:     x <- x * sigmoid(g), element by element
+//   relu_squared:     z -> max(z, 0)^2
+//
+// The lanes, every weighted sum of them and every mean square are 32-bit. A sum over lanes runs in the
+// order of the lanes and a row's reduction in an order that depends on its width only, so a row's result
+// does not depend on what else the launch holds.
+#include "common.cuh"
+
+namespace {
+
+constexpr int LANE_THREADS = 256;
+constexpr int MAX_LANES = 8;
+
+// One block per output row r; source row s = row_index ? row_index[r] : r. `lanes` + l * lane_stride is lane l
+// (a stride of 0: every lane is the same matrix). weight null: y = u, not normalised.
+template <typename TW, typename TY>
+__global__ void __launch_bounds__(LANE_THREADS)
+lanes_rmsnorm_kernel(const float* __restrict__ lanes, long long lane_stride, int count, const float* __restrict__ read,
+                     const TW* __restrict__ weight, TY* __restrict__ y, const int* __restrict__ row_index, int hidden,
+                     float eps) {
+    extern __shared__ float staged[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float square = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += LANE_THREADS) {
+        float sum = 0.f;
+        for (int l = 0; l < count; ++l) {
+            const float value = lanes[l * lane_stride + s * hidden + c];
+            sum = l == 0 ? (read ? read[0] * value : value) : (read ? fmaf(read[l], value, sum) : sum + value);
+        }
+        staged[c] = sum;
+        square = fmaf(sum, sum, square);
+    }
+    float inv = 1.f;
+    if (weight) inv = 1.0f / sqrtf(block_sum<LANE_THREADS>(square, scratch) / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += LANE_THREADS) {
+        const float value = weight ? staged[c] * inv * to_float(weight[c]) : staged[c];
+        y[(long long)r * hidden + c] = from_float<TY>(value);
+    }
+}
+
+// A thread per element of a lane. `source` may be `target` (in place: a thread reads every lane's element
+// before it writes any) or one matrix that stands for every lane (source_stride 0).
+template <typename TY>
+__global__ void lanes_mix_kernel(const float* source, long long source_stride, float* target, long long target_stride,
+                                 int count, const float* __restrict__ mix, const float* __restrict__ write,
+                                 const TY* __restrict__ y, long long total) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    float old[MAX_LANES];
+#pragma unroll
+    for (int l = 0; l < MAX_LANES; ++l)
+        if (l < count) old[l] = source[l * source_stride + index];
+    const float delta = to_float(y[index]);
+#pragma unroll
+    for (int t = 0; t < MAX_LANES; ++t) {
+        if (t >= count) break;
+        float sum = 0.f;
+#pragma unroll
+        for (int l = 0; l < MAX_LANES; ++l)
+            if (l < count) sum = l == 0 ? mix[t] * old[0] : fmaf(mix[l * count + t], old[l], sum);
+        target[t * target_stride + index] = fmaf(write[t], delta, sum);
+    }
+}
+
+// One block per row: both rows staged, their mean squares, then the weighted sum of the two normalised rows.
+template <typename T, typename TY>
+__global__ void __launch_bounds__(LANE_THREADS)
+normed_pair_sum_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ wa,
+                       const float* __restrict__ wb, float ca, float cb, TY* __restrict__ out, int hidden, float eps) {
+    extern __shared__ float staged[];
+    __shared__ float scratch[32];
+    const long long r = blockIdx.x;
+    float* first = staged;
+    float* second = staged + hidden;
+    float square_a = 0.f, square_b = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += LANE_THREADS) {
+        const float x = to_float(a[r * hidden + c]), z = to_float(b[r * hidden + c]);
+        first[c] = x;
+        second[c] = z;
+        square_a = fmaf(x, x, square_a);
+        square_b = fmaf(z, z, square_b);
+    }
+    const float inv_a = 1.0f / sqrtf(block_sum<LANE_THREADS>(square_a, scratch) / (float)hidden + eps);
+    const float inv_b = 1.0f / sqrtf(block_sum<LANE_THREADS>(square_b, scratch) / (float)hidden + eps);
+    for (int c = threadIdx.x; c < hidden; c += LANE_THREADS)
+        out[r * hidden + c] = from_float<TY>(ca * (first[c] * inv_a * wa[c]) + cb * (second[c] * inv_b * wb[c]));
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, long long ldx, const T* __restrict__ gate, long long ldg,
+                                    int width, long long total) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const long long row = index / width;
+    const int c = (int)(index - row * width);
+    const float g = to_float(gate[row * ldg + c]);
+    x[row * ldx + c] = from_float<T>(to_float(x[row * ldx + c]) / (1.0f + expf(-g)));
+}
+
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ z, T* __restrict__ out, long long total) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const float value = fmaxf(to_float(z[index]), 0.f);
+    out[index] = from_float<T>(value * value);
+}
+
+// eight bfloat16 values a thread (16-byte pieces)
+__global__ void relu_squared_bf16x8_kernel(const bf16* __restrict__ z, bf16* __restrict__ out, long long groups) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= groups) return;
+    const uint4 raw = reinterpret_cast<const uint4*>(z)[index];
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    uint4 packed;
+    __nv_bfloat162* result = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 two = __bfloat1622float2(pairs[i]);
+        const float x = fmaxf(two.x, 0.f), w = fmaxf(two.y, 0.f);
+        result[i] = __floats2bfloat162_rn(x * x, w * w);
+    }
+    reinterpret_cast<uint4*>(out)[index] = packed;
+}
+
+template <typename TW>
+int lanes_rmsnorm_out(const float* lanes, long long lane_stride, int count, const float* read, const TW* weight, void* y,
+                      int y_dtype, const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
+    const size_t shared = (size_t)hidden * sizeof(float);
+    if (y_dtype == KIDI_F32) {
+        auto kernel = lanes_rmsnorm_kernel<TW, float>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, lanes, lane_stride, count, read, weight, (float*)y,
+                           row_index, hidden, eps);
+    }
+    if (y_dtype == KIDI_BF16) {
+        auto kernel = lanes_rmsnorm_kernel<TW, bf16>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, lanes, lane_stride, count, read, weight, (bf16*)y,
+                           row_index, hidden, eps);
+    }
+    return KIDI_REFUSED_DTYPE;
+}
+
+template <typename T>
+int normed_pair_sum_out(const T* a, const T* b, const float* wa, const float* wb, float ca, float cb, void* out,
+                        int out_dtype, int rows, int hidden, float eps, cudaStream_t stream) {
+    const size_t shared = (size_t)2 * hidden * sizeof(float);
+    if (out_dtype == KIDI_F32) {
+        auto kernel = normed_pair_sum_kernel<T, float>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, a, b, wa, wb, ca, cb, (float*)out, hidden, eps);
+    }
+    if (out_dtype == KIDI_BF16) {
+        auto kernel = normed_pair_sum_kernel<T, bf16>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, a, b, wa, wb, ca, cb, (bf16*)out, hidden, eps);
+    }
+    return KIDI_REFUSED_DTYPE;
+}
+
+}  // namespace
+
+KIDI_API int kidi_lanes_rmsnorm(const float* lanes, long long lane_stride, int count, const float* read,
+                                const void* weight, int weight_dtype, void* y, int y_dtype, const int* row_index,
+                                int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (count <= 0 || count > MAX_LANES || hidden <= 0 || (size_t)hidden * sizeof(float) > 200 * 1024)
+        return KIDI_REFUSED_SIZE;
+    if (!weight || weight_dtype == KIDI_F32)
+        return lanes_rmsnorm_out<float>(lanes, lane_stride, count, read, (const float*)weight, y, y_dtype, row_index,
+                                        rows, hidden, eps, stream);
+    if (weight_dtype == KIDI_BF16)
+        return lanes_rmsnorm_out<bf16>(lanes, lane_stride, count, read, (const bf16*)weight, y, y_dtype, row_index, rows,
+                                       hidden, eps, stream);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_lanes_mix(const float* source, long long source_stride, float* target, long long target_stride,
+                            int count, const float* mix, const float* write, const void* y, int y_dtype,
+                            long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (count <= 0 || count > MAX_LANES) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (y_dtype == KIDI_F32)
+        return kidi_launch(lanes_mix_kernel<float>, blocks, 256, 0, stream, source, source_stride, target, target_stride,
+                           count, mix, write, (const float*)y, total);
+    if (y_dtype == KIDI_BF16)
+        return kidi_launch(lanes_mix_kernel<bf16>, blocks, 256, 0, stream, source, source_stride, target, target_stride,
+                           count, mix, write, (const bf16*)y, total);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_normed_pair_sum(const void* a, const void* b, int dtype, const float* wa, const float* wb, float ca,
+                                  float cb, void* out, int out_dtype, int rows, int hidden, float eps,
+                                  cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || (size_t)2 * hidden * sizeof(float) > 200 * 1024) return KIDI_REFUSED_SIZE;
+    if (dtype == KIDI_F32)
+        return normed_pair_sum_out<float>((const float*)a, (const float*)b, wa, wb, ca, cb, out, out_dtype, rows, hidden,
+                                          eps, stream);
+    if (dtype == KIDI_BF16)
+        return normed_pair_sum_out<bf16>((const bf16*)a, (const bf16*)b, wa, wb, ca, cb, out, out_dtype, rows, hidden,
+                                         eps, stream);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_sigmoid_gate(void* x, long long ldx, const void* gate, long long ldg, int dtype, int rows, int width,
+                               cudaStream_t stream) {
+    const long long total = (long long)rows * width;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32)
+        return kidi_launch(sigmoid_gate_kernel<float>, blocks, 256, 0, stream, (float*)x, ldx, (const float*)gate, ldg,
+                           width, total);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(sigmoid_gate_kernel<bf16>, blocks, 256, 0, stream, (bf16*)x, ldx, (const bf16*)gate, ldg, width,
+                           total);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_relu_squared(const void* z, void* out, int dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (dtype == KIDI_BF16 && total % 8 == 0 && !((uintptr_t)z & 15) && !((uintptr_t)out & 15)) {
+        const long long groups = total / 8;
+        return kidi_launch(relu_squared_bf16x8_kernel, (unsigned)((groups + 255) / 256), 256, 0, stream, (const bf16*)z,
+                           (bf16*)out, groups);
+    }
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == KIDI_F32)
+        return kidi_launch(relu_squared_kernel<float>, blocks, 256, 0, stream, (const float*)z, (float*)out, total);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(relu_squared_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)z, (bf16*)out, total);
+    return KIDI_REFUSED_DTYPE;
+}

@@ -1,0 +1,434 @@
+// Linear recurrences with a matrix state per head whose decay is one number per head and token:
+//
+//     S_t = a_t S_(t-1) + b_t k_t v_t^T            S: [dim, vdim] (+ one column whose "value" is 1, if asked for)
+//     o_t = S_t^T q_t
+//
+// a_t (decay) and b_t (write strength) come computed, in 32-bit, from a gate kernel of the mixer that owns the
+// recurrence; k, q (per head, or per group of heads) and v are columns of the mixer's projections. Two mixers
+// are served, each with its gate kernel and its finishing kernel:
+//
+//  * a selective state-space mixer (Mamba-2): a = exp(-exp(A_log) dt), b = dt, dt = softplus(dt~ + bias), k = B,
+//    q = C, v = x after a short causal convolution with SiLU; y = (o + D x) silu(z), RMS-normed in equal parts.
+//  * a matrix memory with exponential gates (mLSTM): log gates i = cap tanh(i~ / cap), f = logsigmoid(cap
+//    tanh(f~ / cap)), a running maximum m_t = max(f_t + m_(t-1), i_t) (m_0 = 0), a = exp(f + m_(t-1) - m_t),
+//    b = exp(i - m_t); the extra state column is the normaliser n_t = a n_(t-1) + b k_t;
+//    o <- o / (max(|n . q|, exp(-m_t)) + 1e-6), RMS-normed per head, times a weight, times sigmoid(g).
+//
+// The state lives in 32-bit floats per cache slot and is carried from token to token; gates, decays, the state,
+// the read-out and the norms are 32-bit. The columns of a head's state are independent, so a block takes 32
+// columns of one (sequence, head) and walks the sequence's rows of the step in order: a token's result depends on
+// the sizes only, not on what else is in the step, nor on how the sequence was cut into steps.
+#include "common.cuh"
+
+struct ScalarRecurrenceArgs {
+    const void* k;         // [rows, ldk]: key head j at j * dim
+    long long ldk;
+    const void* q;         // [rows, ldq]: query head j at j * dim
+    long long ldq;
+    const void* v;         // [rows, ldv]: value head h at h * vdim
+    long long ldv;
+    const float* coef;     // [rows, heads, coef_width]: a_t, b_t first
+    float* state;          // [slots + 1, heads, dim, vdim + extra]
+    float* out;            // [rows, heads * (vdim + extra)]: the read-out; column vdim of a head: n . q
+    const int* row_seq;    // [rows] (-1: padding)
+    const int* seq_slot;   // [seqs]
+    const int* seq_row0;   // [seqs]
+    const int* seq_len;    // [seqs]
+    int seqs, heads, k_heads, q_heads, dim, vdim, extra, coef_width;
+    float q_scale;         // q is multiplied by it
+};
+
+struct ShortConvArgs {
+    const void* x;         // [rows, ldx]: the channels' inputs
+    long long ldx;
+    const float* weight;   // [channels, taps]: the last column multiplies the current token
+    const float* bias;     // [channels] or null
+    void* state;           // [slots + 1, taps - 1, channels]: a sequence's last taps - 1 inputs (zeros before its start)
+    void* out;             // [rows, ldo]
+    long long ldo;
+    const int* row_seq;
+    const int* row_pos;
+    const int* seq_slot;
+    const int* seq_start;
+    const int* seq_row0;
+    const int* seq_len;
+    int rows, seqs, channels, taps, silu;
+};
+
+namespace {
+
+constexpr int THREADS = 256;
+constexpr int COLUMNS = 32;
+constexpr int GROUPS = THREADS / COLUMNS;
+constexpr int MAX_CHUNK = 16;
+constexpr int MAX_TAPS = 32;
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
+
+// R: state rows a thread keeps in registers (dim <= GROUPS * R).
+template <typename T, int R>
+__global__ void __launch_bounds__(THREADS) scalar_recurrence_kernel(ScalarRecurrenceArgs a) {
+    constexpr int PADDED = GROUPS * R;
+    constexpr int CHUNK = R >= 32 ? MAX_CHUNK / 2 : MAX_CHUNK;     // tokens staged at a time (48 KB of shared memory)
+    __shared__ float keys[CHUNK][PADDED];        // b_t k_t
+    __shared__ float queries[CHUNK][PADDED];     // q_t * q_scale
+    __shared__ float values[CHUNK][COLUMNS];
+    __shared__ float decay[CHUNK];
+    __shared__ float partial[CHUNK][GROUPS][COLUMNS];
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int row0 = a.seq_row0[seq], count = a.seq_len[seq];
+    if (count <= 0 || a.row_seq[row0] < 0) return;        // a padding sequence touches no state
+    const int dim = a.dim, vdim = a.vdim, vcols = a.vdim + a.extra;
+    const int lane = threadIdx.x % COLUMNS, g = threadIdx.x / COLUMNS;
+    const int column = blockIdx.z * COLUMNS + lane;
+    const bool live = column < vcols;
+    const int k_head = head / (a.heads / a.k_heads), q_head = head / (a.heads / a.q_heads);
+    float* state = a.state + ((long long)a.seq_slot[seq] * a.heads + head) * dim * vcols;
+    float S[R];
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const int d = g * R + j;
+        S[j] = live && d < dim ? state[(long long)d * vcols + column] : 0.f;
+    }
+    for (int t0 = 0; t0 < count; t0 += CHUNK) {
+        const int tokens = min(CHUNK, count - t0);
+        for (int index = threadIdx.x; index < tokens * PADDED; index += THREADS) {
+            const int t = index / PADDED, d = index - t * PADDED;
+            const long long row = row0 + t0 + t;
+            float key = 0.f, query = 0.f;
+            if (d < dim) {
+                const float write = a.coef[(row * a.heads + head) * a.coef_width + 1];
+                key = write * to_float(((const T*)a.k)[row * a.ldk + (long long)k_head * dim + d]);
+                query = a.q_scale * to_float(((const T*)a.q)[row * a.ldq + (long long)q_head * dim + d]);
+            }
+            keys[t][d] = key;
+            queries[t][d] = query;
+        }
+        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS) {
+            const int t = index / COLUMNS, c = index - t * COLUMNS;
+            const int col = blockIdx.z * COLUMNS + c;
+            const long long row = row0 + t0 + t;
+            float value = 0.f;
+            if (col < vdim) value = to_float(((const T*)a.v)[row * a.ldv + (long long)head * vdim + col]);
+            else if (col < vcols) value = 1.f;
+            values[t][c] = value;
+        }
+        if (threadIdx.x < tokens)
+            decay[threadIdx.x] = a.coef[((long long)(row0 + t0 + threadIdx.x) * a.heads + head) * a.coef_width];
+        __syncthreads();
+        for (int t = 0; t < tokens; ++t) {
+            const float keep = decay[t], value = values[t][lane];
+            const float* key = &keys[t][g * R];            // one address a group of lanes: broadcasts
+            const float* query = &queries[t][g * R];
+            float sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                const float s = fmaf(keep, S[j], key[j] * value);
+                S[j] = s;
+                sum = fmaf(s, query[j], sum);
+            }
+            partial[t][g][lane] = sum;
+        }
+        __syncthreads();
+        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS) {
+            const int t = index / COLUMNS, c = index - t * COLUMNS;
+            const int col = blockIdx.z * COLUMNS + c;
+            if (col >= vcols) continue;
+            float total = 0.f;
+#pragma unroll
+            for (int k = 0; k < GROUPS; ++k) total += partial[t][k][c];
+            a.out[((long long)(row0 + t0 + t) * a.heads + head) * vcols + col] = total;
+        }
+        // (the next chunk's staging writes keys, queries, values and decay, which nobody reads any more; its walk
+        // writes `partial` only behind the next barrier)
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+        const int d = g * R + j;
+        if (live && d < dim) state[(long long)d * vcols + column] = S[j];
+    }
+}
+
+template <typename T, int R>
+int launch_recurrence(const ScalarRecurrenceArgs& a, cudaStream_t stream) {
+    dim3 grid(a.seqs, a.heads, (a.vdim + a.extra + COLUMNS - 1) / COLUMNS);
+    return kidi_launch(scalar_recurrence_kernel<T, R>, grid, THREADS, 0, stream, a);
+}
+
+template <typename T>
+int dispatch_recurrence(const ScalarRecurrenceArgs& a, cudaStream_t stream) {
+    const int rows = (a.dim + GROUPS - 1) / GROUPS;
+    if (rows <= 1) return launch_recurrence<T, 1>(a, stream);
+    if (rows <= 2) return launch_recurrence<T, 2>(a, stream);
+    if (rows <= 4) return launch_recurrence<T, 4>(a, stream);
+    if (rows <= 8) return launch_recurrence<T, 8>(a, stream);
+    if (rows <= 16) return launch_recurrence<T, 16>(a, stream);
+    if (rows <= 32) return launch_recurrence<T, 32>(a, stream);
+    return KIDI_REFUSED_SIZE;
+}
+
+// ---------------------------------------------------------------- short causal convolution with carried inputs
+// A thread per (row, channel): y = bias + sum_j w[c, j] x(position - (taps - 1) + j), inputs of earlier steps from
+// the state, inputs before the sequence's start zero; then SiLU if asked. The sum is 32-bit.
+template <typename T>
+__global__ void short_conv_kernel(ShortConvArgs a) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= (long long)a.rows * a.channels) return;
+    const int row = (int)(index / a.channels), c = (int)(index - (long long)row * a.channels);
+    const int seq = a.row_seq[row];
+    if (seq < 0) return;
+    const int position = a.row_pos[row], start = a.seq_start[seq], row0 = a.seq_row0[seq];
+    const int reach = a.taps - 1;
+    const T* state = (const T*)a.state + (long long)a.seq_slot[seq] * reach * a.channels;
+    float sum = a.bias ? a.bias[c] : 0.f;
+    for (int j = 0; j < a.taps; ++j) {
+        const int p = position - reach + j;
+        float x = 0.f;
+        if (p >= start) x = to_float(((const T*)a.x)[(long long)(row0 + p - start) * a.ldx + c]);
+        else if (p >= 0) x = to_float(state[(long long)(p - start + reach) * a.channels + c]);
+        sum = fmaf(a.weight[(long long)c * a.taps + j], x, sum);
+    }
+    ((T*)a.out)[(long long)row * a.ldo + c] = from_float<T>(a.silu ? silu(sum) : sum);
+}
+
+// After the convolution: a sequence's last taps - 1 inputs, from the step's rows and (a step shorter than that) from
+// what the state held. A thread per (sequence, channel) reads all it needs before it writes.
+template <typename T>
+__global__ void short_conv_state_kernel(ShortConvArgs a) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= (long long)a.seqs * a.channels) return;
+    const int seq = (int)(index / a.channels), c = (int)(index - (long long)seq * a.channels);
+    const int row0 = a.seq_row0[seq], count = a.seq_len[seq];
+    if (count <= 0 || a.row_seq[row0] < 0) return;
+    const int reach = a.taps - 1;
+    T* state = (T*)a.state + (long long)a.seq_slot[seq] * reach * a.channels;
+    T kept[MAX_TAPS];
+    for (int j = 0; j < reach; ++j) {
+        const int back = reach - j;            // the input `back` tokens before the sequence's new end
+        kept[j] = back <= count ? ((const T*)a.x)[(long long)(row0 + count - back) * a.ldx + c]
+                                : state[(long long)(j + count) * a.channels + c];
+    }
+    for (int j = 0; j < reach; ++j) state[(long long)j * a.channels + c] = kept[j];
+}
+
+// ---------------------------------------------------------------- the state-space mixer's gates and finish
+// coef[row, head] = (exp(-exp(A_log) dt), dt), dt = softplus(dt~ + bias) (no clamp).
+template <typename T>
+__global__ void state_space_gates_kernel(const T* __restrict__ dt, long long ld, const float* __restrict__ dt_bias,
+                                         const float* __restrict__ a_log, float* __restrict__ coef, int rows, int heads) {
+    const int index = blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= rows * heads) return;
+    const int row = index / heads, head = index - row * heads;
+    const float raw = to_float(dt[(long long)row * ld + head]) + dt_bias[head];
+    const float step = raw > 20.f ? raw : log1pf(expf(raw));
+    coef[2 * index] = expf(-expf(a_log[head]) * step);
+    coef[2 * index + 1] = step;
+}
+
+// A block per (row, part): y = (o + D x) silu(z) over the part's entries, divided by its root mean square, times
+// the weight.
+template <typename T>
+__global__ void __launch_bounds__(THREADS)
+state_space_finish_kernel(const float* __restrict__ read, const T* __restrict__ x, long long ldx, const T* __restrict__ z,
+                          long long ldz, const float* __restrict__ skip, const float* __restrict__ weight,
+                          T* __restrict__ out, long long ldo, int vdim, int part, float eps) {
+    extern __shared__ float staged[];
+    __shared__ float scratch[32];
+    const long long row = blockIdx.x;
+    const int begin = blockIdx.y * part;
+    const int inner = gridDim.y * part;
+    float square = 0.f;
+    for (int i = threadIdx.x; i < part; i += THREADS) {
+        const int c = begin + i;
+        const float value = to_float(x[row * ldx + c]);
+        const float y = (read[row * inner + c] + skip[c / vdim] * value) * silu(to_float(z[row * ldz + c]));
+        staged[i] = y;
+        square = fmaf(y, y, square);
+    }
+    const float inv = 1.0f / sqrtf(block_sum<THREADS>(square, scratch) / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += THREADS)
+        out[row * ldo + begin + i] = from_float<T>(staged[i] * inv * weight[begin + i]);
+}
+
+// ---------------------------------------------------------------- the matrix memory's gates and finish
+// A warp per (sequence, head) walks the sequence's rows 32 at a time: each lane computes its token's log gates,
+// the running maximum m_t = max(f_t + m_(t-1), i_t) is a scan of the maps m -> max(m + F, I) (composed:
+// (F1, I1) then (F2, I2) = (F1 + F2, max(I1 + F2, I2))), and coef[row, head] = (exp(f + m_(t-1) - m_t),
+// exp(i - m_t), exp(-m_t)). m is carried in `maximum` [slots + 1, heads].
+template <typename T>
+__global__ void matrix_memory_gates_kernel(const T* __restrict__ gates, long long ld, int offset_i, int offset_f,
+                                           float cap, float* __restrict__ coef, float* __restrict__ maximum,
+                                           const int* __restrict__ row_seq, const int* __restrict__ seq_slot,
+                                           const int* __restrict__ seq_row0, const int* __restrict__ seq_len, int seqs,
+                                           int heads) {
+    const int item = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (item >= seqs * heads) return;
+    const int seq = item / heads, head = item - seq * heads;
+    const int row0 = seq_row0[seq], count = seq_len[seq];
+    if (count <= 0 || row_seq[row0] < 0) return;
+    float* kept = maximum + (long long)seq_slot[seq] * heads + head;
+    float m = *kept;
+    for (int t0 = 0; t0 < count; t0 += 32) {
+        const int t = t0 + lane;
+        const bool live = t < count;
+        float log_in = -INFINITY, log_keep = 0.f;      // beyond the end: the identity map
+        if (live) {
+            const T* row = gates + (long long)(row0 + t) * ld;
+            log_in = cap * tanhf(to_float(row[offset_i + head]) / cap);
+            const float bounded = cap * tanhf(to_float(row[offset_f + head]) / cap);
+            log_keep = fminf(bounded, 0.f) - log1pf(expf(-fabsf(bounded)));      // log sigmoid
+        }
+        float F = log_keep, I = log_in;
+#pragma unroll
+        for (int step = 1; step < 32; step <<= 1) {
+            const float F_before = __shfl_up_sync(0xffffffffu, F, step), I_before = __shfl_up_sync(0xffffffffu, I, step);
+            if (lane >= step) {
+                I = fmaxf(I_before + F, I);
+                F = F_before + F;
+            }
+        }
+        const float now = fmaxf(m + F, I);
+        float before = __shfl_up_sync(0xffffffffu, now, 1);
+        if (lane == 0) before = m;
+        if (live) {
+            float* target = coef + ((long long)(row0 + t) * heads + head) * 3;
+            target[0] = expf(log_keep + before - now);
+            target[1] = expf(log_in - now);
+            target[2] = expf(-now);
+        }
+        m = __shfl_sync(0xffffffffu, now, min(31, count - t0 - 1));
+    }
+    if (lane == 0) *kept = m;
+}
+
+// A warp per (row, head): o / (max(|n . q|, exp(-m)) + 1e-6), divided by its root mean square over vdim, times the
+// weight, times sigmoid(g).
+template <typename T>
+__global__ void matrix_memory_finish_kernel(const float* __restrict__ read, const float* __restrict__ coef,
+                                            const float* __restrict__ weight, const T* __restrict__ gate, long long ldg,
+                                            T* __restrict__ out, long long ldo, long long items, int heads, int vdim,
+                                            float eps) {
+    const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const long long row = item / heads;
+    const int head = (int)(item - row * heads);
+    const float* source = read + item * (vdim + 1);
+    const float denominator = fmaxf(fabsf(source[vdim]), coef[item * 3 + 2]) + 1e-6f;
+    float square = 0.f;
+    for (int c = lane; c < vdim; c += 32) {
+        const float value = source[c] / denominator;
+        square = fmaf(value, value, square);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(square) / (float)vdim + eps);
+    for (int c = lane; c < vdim; c += 32) {
+        const int column = head * vdim + c;
+        const float g = to_float(gate[row * ldg + column]);
+        out[row * ldo + column] = from_float<T>(source[c] / denominator * inv * weight[column] / (1.0f + expf(-g)));
+    }
+}
+
+}  // namespace
+
+KIDI_API int kidi_scalar_recurrence(const ScalarRecurrenceArgs* args, int dtype, cudaStream_t stream) {
+    const ScalarRecurrenceArgs& a = *args;
+    if (a.seqs <= 0) return 0;
+    if (a.heads <= 0 || a.heads > 65535 || a.dim <= 0 || a.vdim <= 0 || a.extra < 0 || a.extra > 1 || a.k_heads <= 0 ||
+        a.q_heads <= 0 || a.heads % a.k_heads || a.heads % a.q_heads || a.coef_width < 2 ||
+        (a.vdim + a.extra + COLUMNS - 1) / COLUMNS > 65535)
+        return KIDI_REFUSED_SIZE;
+    if (dtype == KIDI_F32) return dispatch_recurrence<float>(a, stream);
+    if (dtype == KIDI_BF16) return dispatch_recurrence<bf16>(a, stream);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_short_conv(const ShortConvArgs* args, int dtype, cudaStream_t stream) {
+    const ShortConvArgs& a = *args;
+    if (a.rows <= 0) return 0;
+    if (a.channels <= 0 || a.taps < 1 || a.taps > MAX_TAPS) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)(((long long)a.rows * a.channels + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(short_conv_kernel<float>, blocks, 256, 0, stream, a);
+    if (dtype == KIDI_BF16) return kidi_launch(short_conv_kernel<bf16>, blocks, 256, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_short_conv_state(const ShortConvArgs* args, int dtype, cudaStream_t stream) {
+    const ShortConvArgs& a = *args;
+    if (a.seqs <= 0 || a.taps <= 1) return 0;
+    if (a.channels <= 0 || a.taps > MAX_TAPS) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)(((long long)a.seqs * a.channels + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(short_conv_state_kernel<float>, blocks, 256, 0, stream, a);
+    if (dtype == KIDI_BF16) return kidi_launch(short_conv_state_kernel<bf16>, blocks, 256, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_state_space_gates(const void* dt, long long ld, int dtype, const float* dt_bias, const float* a_log,
+                                    float* coef, int rows, int heads, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (heads <= 0 || (long long)rows * heads > 0x7fffffff) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)((rows * heads + 255) / 256);
+    if (dtype == KIDI_F32)
+        return kidi_launch(state_space_gates_kernel<float>, blocks, 256, 0, stream, (const float*)dt, ld, dt_bias, a_log,
+                           coef, rows, heads);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(state_space_gates_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)dt, ld, dt_bias, a_log,
+                           coef, rows, heads);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_state_space_finish(const float* read, const void* x, long long ldx, const void* z, long long ldz,
+                                     int dtype, const float* skip, const float* weight, void* out, long long ldo,
+                                     int rows, int heads, int vdim, int parts, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int inner = heads * vdim;
+    if (heads <= 0 || vdim <= 0 || parts <= 0 || inner % parts || parts > 65535) return KIDI_REFUSED_SIZE;
+    const int part = inner / parts;
+    const size_t shared = (size_t)part * sizeof(float);
+    if (shared > 200 * 1024) return KIDI_REFUSED_SIZE;
+    dim3 grid(rows, parts);
+    if (dtype == KIDI_F32) {
+        auto kernel = state_space_finish_kernel<float>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, grid, THREADS, shared, stream, read, (const float*)x, ldx, (const float*)z, ldz, skip,
+                           weight, (float*)out, ldo, vdim, part, eps);
+    }
+    if (dtype == KIDI_BF16) {
+        auto kernel = state_space_finish_kernel<bf16>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, grid, THREADS, shared, stream, read, (const bf16*)x, ldx, (const bf16*)z, ldz, skip,
+                           weight, (bf16*)out, ldo, vdim, part, eps);
+    }
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_matrix_memory_gates(const void* gates, long long ld, int offset_i, int offset_f, int dtype, float cap,
+                                      float* coef, float* maximum, const int* row_seq, const int* seq_slot,
+                                      const int* seq_row0, const int* seq_len, int seqs, int heads,
+                                      cudaStream_t stream) {
+    if (seqs <= 0) return 0;
+    if (heads <= 0 || !(cap > 0.f)) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)(((long long)seqs * heads * 32 + 127) / 128);
+    if (dtype == KIDI_F32)
+        return kidi_launch(matrix_memory_gates_kernel<float>, blocks, 128, 0, stream, (const float*)gates, ld, offset_i,
+                           offset_f, cap, coef, maximum, row_seq, seq_slot, seq_row0, seq_len, seqs, heads);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(matrix_memory_gates_kernel<bf16>, blocks, 128, 0, stream, (const bf16*)gates, ld, offset_i,
+                           offset_f, cap, coef, maximum, row_seq, seq_slot, seq_row0, seq_len, seqs, heads);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_matrix_memory_finish(const float* read, const float* coef, const float* weight, const void* gate,
+                                       long long ldg, int dtype, void* out, long long ldo, int rows, int heads, int vdim,
+                                       float eps, cudaStream_t stream) {
+    const long long items = (long long)rows * heads;
+    if (items <= 0) return 0;
+    if (vdim <= 0) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)((items * 32 + 127) / 128);
+    if (dtype == KIDI_F32)
+        return kidi_launch(matrix_memory_finish_kernel<float>, blocks, 128, 0, stream, read, coef, weight,
+                           (const float*)gate, ldg, (float*)out, ldo, items, heads, vdim, eps);
+    if (dtype == KIDI_BF16)
+        return kidi_launch(matrix_memory_finish_kernel<bf16>, blocks, 128, 0, stream, read, coef, weight,
+                           (const bf16*)gate, ldg, (bf16*)out, ldo, items, heads, vdim, eps);
+    return KIDI_REFUSED_DTYPE;
+}

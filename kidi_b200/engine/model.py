@@ -30,6 +30,9 @@ from ..parts import stream_mix as _stream_mix  # noqa: F401
 from ..parts import token_input as _token_input  # noqa: F401
 from ..parts import differential_attention as _differential_attention  # noqa: F401
 from ..parts import routed as _routed  # noqa: F401
+from ..parts import state_space as _state_space  # noqa: F401
+from ..parts import matrix_memory as _matrix_memory  # noqa: F401
+from ..parts import parallel_mixers as _parallel_mixers  # noqa: F401
 
 
 class CausalLM:

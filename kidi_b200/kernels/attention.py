@@ -96,7 +96,7 @@ def tensor_memory_fits(qkv: torch.Tensor, out: torch.Tensor, head_dim: int, head
 class PromptCache(ctypes.Structure):
     """Where the keys and values lie when prompts continue cached sequences (KidiPromptCache)."""
     _fields_ = [("keys", c_void_p), ("values", c_void_p), ("rows", c_longlong), ("table", c_void_p),
-                ("pages_per_seq", c_int), ("seq_start", c_void_p), ("seq_slot", c_void_p)]
+                ("pages_per_seq", c_int), ("seq_start", c_void_p), ("seq_slot", c_void_p), ("q_only", c_int)]
 
 
 class HeadExtras(ctypes.Structure):
@@ -115,11 +115,12 @@ def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.T
                           seqs: int, max_new: int, *, heads: int, kv_heads: int, head_dim: int, scale: float,
                           window: int, kv_view=None, seq_start: Optional[torch.Tensor] = None,
                           seq_slot: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                          gate: Optional[torch.Tensor] = None) -> None:
+                          gate: Optional[torch.Tensor] = None, q_only: bool = False) -> None:
     """Causal attention of packed prompts. Without `kv_view` the prompts start at position 0
     and every key is a row of qkv; with it (a cache of 64-token pages without a ring, into
     which the step's rows have been written) every key and value is read from the cache,
-    so the prompts may continue sequences of `seq_start` tokens. `sinks`, `gate`: see `run`."""
+    so the prompts may continue sequences of `seq_start` tokens. `sinks`, `gate`: see `run`. `q_only` (with
+    `kv_view`): the rows of qkv hold the query heads only."""
     lib = tensor_memory_library(head_dim)
     cache = extras = None
     if sinks is not None or gate is not None:
@@ -127,7 +128,8 @@ def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.T
                             gate.stride(0) if gate is not None else 0)
     if kv_view is not None:
         cache = PromptCache(kv_view.keys.data_ptr(), kv_view.values.data_ptr(), kv_view.keys.numel() // head_dim,
-                            kv_view.table.data_ptr(), kv_view.table.shape[1], seq_start.data_ptr(), seq_slot.data_ptr())
+                            kv_view.table.data_ptr(), kv_view.table.shape[1], seq_start.data_ptr(), seq_slot.data_ptr(),
+                            1 if q_only else 0)
     _check(lib.kidi_attention_prefill_tcgen05(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), out.stride(0), seq_len.data_ptr(),
         seq_row0.data_ptr(), seqs, max_new, heads, kv_heads, int(window or 0), float(scale),
@@ -242,7 +244,7 @@ def fuses_rotation(plan, qkv: torch.Tensor, *, heads: int, kv_heads: int, head_d
 def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, keys_in_step, rotation=None,
         step_rows_cached: bool = False, splits: Optional[int] = None, ring: Optional[bool] = None,
         softcap: float = 0.0, slopes: Optional[torch.Tensor] = None, value_dim: Optional[int] = None,
-        sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
+        sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, q_only: bool = False) -> None:
     """`ctx` gives the step's `plan`, its device `tables` and `workspace(name, count, zero)`.
     `keys_in_step`: the step's own keys and values are read from qkv (else from the
     cache, like the earlier ones). `step_rows_cached`: they are in the cache as well (a cache
@@ -252,7 +254,8 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     and, with `store`, writes the step's key and value to the cache. `splits` and `ring`
     override the launcher's own choice of the decode kernel's form (tests of each form).
     `value_dim`, `sinks`, `gate`: value heads of another width than the keys, a number per head in the softmax
-    denominator, a sigmoid gate per row and head (see `ops.attention_generic`)."""
+    denominator, a sigmoid gate per row and head (see `ops.attention_generic`). `q_only`: the rows of qkv hold the
+    query heads only (every key and value comes from the cache)."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
     # Scores that are bounded or shifted by position run on the general kernel (the tensor-core kernels
@@ -277,7 +280,7 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         if (kv_view is not None and (step_rows_cached or not keys_in_step) and kv_view.ring_pages == 0
                 and kv_view.page_size == 64 and kv_view.keys.is_contiguous() and kv_view.table.is_contiguous()):
             prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, kv_view=kv_view,
-                                  seq_start=tables.seq_start, seq_slot=tables.seq_slot, **common)
+                                  seq_start=tables.seq_start, seq_slot=tables.seq_slot, q_only=q_only, **common)
             return
     item = qkv.element_size()
     args = FastAttentionArgs(

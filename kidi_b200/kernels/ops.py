@@ -184,6 +184,17 @@ def core():
         lib.kidi_tanh_cap.argtypes = [c_void_p, c_longlong, c_float, c_void_p]
         for name in ("kidi_add_table_rows", "kidi_bounded_gate", "kidi_tanh_cap"):
             getattr(lib, name).restype = c_int
+        lib.kidi_lanes_rmsnorm.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                           c_void_p, c_int, c_int, c_float, c_void_p]
+        lib.kidi_lanes_mix.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_longlong, c_void_p]
+        lib.kidi_normed_pair_sum.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                                             c_int, c_int, c_int, c_float, c_void_p]
+        lib.kidi_sigmoid_gate.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]
+        lib.kidi_relu_squared.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
+        for name in ("kidi_lanes_rmsnorm", "kidi_lanes_mix", "kidi_normed_pair_sum", "kidi_sigmoid_gate",
+                     "kidi_relu_squared"):
+            getattr(lib, name).restype = c_int
         for name in ("kidi_add_layernorm", "kidi_rms_rows", "kidi_poly_norm", "kidi_token_gate", "kidi_add_normed_mix",
                      "kidi_add_cast", "kidi_gemm_simt_batched"):
             getattr(lib, name).restype = c_int
@@ -207,7 +218,7 @@ class RopeStoreArgs(ctypes.Structure):
                 ("seq_slot", c_void_p), ("seq_start", c_void_p), ("seq_len", c_void_p), ("k_cache", c_void_p),
                 ("v_cache", c_void_p), ("cache", CacheGeometry), ("rows", c_int), ("heads", c_int),
                 ("kv_heads", c_int), ("head_dim", c_int), ("rotary_dim", c_int), ("eps", c_float), ("transform", c_int),
-                ("value_dim", c_int)]
+                ("value_dim", c_int), ("q_scale", c_void_p)]
 
 
 class AttentionArgs(ctypes.Structure):
@@ -497,6 +508,88 @@ def add_table_rows(x: torch.Tensor, table: torch.Tensor, index: torch.Tensor, sc
                                       table.shape[0], float(scale), _stream()), "add_table_rows")
 
 
+def lanes_rmsnorm(lanes: torch.Tensor, read: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                  out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """u = sum_s read[s] * lanes[s] (`read` None: the plain sum), y = u / sqrt(mean(u^2) + eps) * weight (`weight`
+    None: y = u). `lanes` is float32 [count, rows, hidden], each lane contiguous (an expanded view of one matrix
+    will do). With `row_index`, row r of the output comes from row row_index[r]."""
+    _need_cuda(lanes, read, weight, row_index)
+    if lanes.dtype != torch.float32 or lanes.dim() != 3 or lanes.stride(2) != 1 or lanes.stride(1) != lanes.shape[2]:
+        raise invalid_argument("lanes_rmsnorm takes float32 lanes [count, rows, hidden] with contiguous matrices")
+    count, rows_in, hidden = lanes.shape
+    _float_vector(read, count, "the lanes' read weights")
+    if weight is not None and (weight.shape != (hidden,) or not weight.is_contiguous()):
+        raise invalid_argument(f"the norm weight must have {hidden} elements")
+    if row_index is not None and (row_index.dtype != torch.int32 or row_index.dim() != 1):
+        raise invalid_argument("row_index must be an int32 vector")
+    rows = row_index.shape[0] if row_index is not None else rows_in
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=lanes.device)
+    _check(core().kidi_lanes_rmsnorm(_ptr(lanes), lanes.stride(0), count, _ptr(read), _ptr(weight),
+                                     dtype_code(weight.dtype) if weight is not None else NONE, _ptr(out),
+                                     dtype_code(out_dtype), _ptr(row_index), rows, hidden, float(eps), _stream()),
+           "lanes_rmsnorm")
+    return out
+
+
+def lanes_mix(source: torch.Tensor, target: torch.Tensor, mix: torch.Tensor, write: torch.Tensor,
+              y: torch.Tensor) -> torch.Tensor:
+    """target[t] = sum_s mix[s, t] * source[s] + write[t] * y for float32 lanes [count, rows, hidden]; `source` may
+    be `target` itself, or an expanded view of one matrix. mix float32 [count, count] ([from, to]), write float32
+    [count], y [rows, hidden] of any element type."""
+    _need_cuda(source, target, mix, write, y)
+    count = target.shape[0]
+    for lanes in (source, target):
+        if lanes.dtype != torch.float32 or lanes.dim() != 3 or lanes.shape != target.shape or lanes.stride(2) != 1 \
+                or lanes.stride(1) != lanes.shape[2]:
+            raise invalid_argument("lanes_mix takes float32 lanes [count, rows, hidden] with contiguous matrices")
+    if mix.dtype != torch.float32 or mix.shape != (count, count) or not mix.is_contiguous():
+        raise invalid_argument("lanes_mix: the mixing matrix is float32 [count, count]")
+    _float_vector(write, count, "the lanes' write weights")
+    if y.shape != target.shape[1:] or not y.is_contiguous():
+        raise invalid_argument("lanes_mix: y must be a contiguous matrix of a lane's shape")
+    _check(core().kidi_lanes_mix(_ptr(source), source.stride(0), _ptr(target), target.stride(0), count, _ptr(mix),
+                                 _ptr(write), _ptr(y), dtype_code(y.dtype), y.numel(), _stream()), "lanes_mix")
+    return target
+
+
+def normed_pair_sum(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float,
+                    share_a: float = 0.5, share_b: float = 0.5, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """share_a * a / rms(a) * weight_a + share_b * b / rms(b) * weight_b over each row (32-bit arithmetic)."""
+    _need_cuda(a, b, weight_a, weight_b)
+    if a.dim() != 2 or a.shape != b.shape or a.dtype != b.dtype or not a.is_contiguous() or not b.is_contiguous():
+        raise invalid_argument("normed_pair_sum takes two contiguous matrices of one shape and type")
+    rows, hidden = a.shape
+    _float_vector(weight_a, hidden, "the first norm weight")
+    _float_vector(weight_b, hidden, "the second norm weight")
+    out = torch.empty((rows, hidden), dtype=out_dtype, device=a.device)
+    _check(core().kidi_normed_pair_sum(_ptr(a), _ptr(b), dtype_code(a.dtype), _ptr(weight_a), _ptr(weight_b),
+                                       float(share_a), float(share_b), _ptr(out), dtype_code(out_dtype), rows, hidden,
+                                       float(eps), _stream()), "normed_pair_sum")
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """x *= sigmoid(gate) element by element, in place; x and gate [rows, width] of one type (views whose last axis
+    is contiguous); sigmoid and product in 32-bit."""
+    _need_cuda(x, gate)
+    if x.dim() != 2 or x.shape != gate.shape or x.dtype != gate.dtype or x.stride(1) != 1 or gate.stride(1) != 1:
+        raise invalid_argument("sigmoid_gate takes two [rows, width] matrices of one type")
+    _check(core().kidi_sigmoid_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), dtype_code(x.dtype), x.shape[0],
+                                    x.shape[1], _stream()), "sigmoid_gate")
+    return x
+
+
+def relu_squared(z: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """max(z, 0)^2 element by element; `out` may be z itself."""
+    _need_cuda(z, out)
+    if not z.is_contiguous() or (out is not None and (out.shape != z.shape or out.dtype != z.dtype or not out.is_contiguous())):
+        raise invalid_argument("relu_squared takes a contiguous tensor")
+    if out is None:
+        out = torch.empty_like(z)
+    _check(core().kidi_relu_squared(_ptr(z), _ptr(out), dtype_code(z.dtype), z.numel(), _stream()), "relu_squared")
+    return out
+
+
 def tanh_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
     """x <- cap * tanh(x / cap), float32, in place."""
     _need_cuda(x)
@@ -559,12 +652,14 @@ def gemm_simt(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype,
 def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q_norm: Optional[torch.Tensor],
                k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                rotary_dim: int, tables, kv_view, store: bool, transform: bool = True,
-               value_dim: Optional[int] = None) -> None:
+               value_dim: Optional[int] = None, q_scale: Optional[torch.Tensor] = None) -> None:
     """In place on qkv [rows, (heads + kv_heads) * head_dim + kv_heads * value_dim (+ columns that are left
     alone)]: per-head RMSNorm and rotation of the q and k heads; k and v heads are also written to the cache when
     `store` is set. With `transform=False` nothing is normalised or rotated: the k and v
     heads are only copied to the cache. `tables` is the step's `DeviceTables`. `value_dim` (default head_dim) is
-    the width of a v head."""
+    the width of a v head. `q_scale` (float32 [positions]): a q head at position p is multiplied by q_scale[p] after
+    its norm and rotation. With `kv_heads` 0 the rows hold q heads only (a layer that reads another layer's keys
+    and values) and nothing is stored."""
     _need_cuda(qkv)
     rows = qkv.shape[0]
     value_dim = head_dim if value_dim is None else int(value_dim)
@@ -577,7 +672,9 @@ def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q
         raise invalid_argument("rope_store: the head norms must have head_dim elements and one type")
     if cos is not None and (cos.dtype != torch.float32 or cos.shape[1] != rotary_dim // 2 or sin.shape != cos.shape):
         raise invalid_argument("rope_store: the rotation tables must be float32 [positions, rotary_dim/2]")
-    view = kv_view if store else None
+    if q_scale is not None and (q_scale.dtype != torch.float32 or q_scale.dim() != 1 or not q_scale.is_contiguous()):
+        raise invalid_argument("rope_store: the query scale is a float32 vector with an entry per position")
+    view = kv_view if store and kv_heads > 0 else None
     if view is not None and view.keys.dtype != qkv.dtype:
         raise invalid_argument("rope_store: the cache and the activations differ in element type")
     args = RopeStoreArgs(
@@ -586,7 +683,7 @@ def rope_store(qkv: torch.Tensor, *, heads: int, kv_heads: int, head_dim: int, q
         tables.seq_start.data_ptr(), tables.seq_len.data_ptr(),
         view.keys.data_ptr() if view is not None else 0, view.values.data_ptr() if view is not None else 0,
         cache_geometry(view, kv_heads, head_dim), rows, heads, kv_heads, head_dim, rotary_dim, float(eps),
-        1 if transform else 0, value_dim)
+        1 if transform else 0, value_dim, _ptr(q_scale))
     _check(core().kidi_rope_store(ctypes.byref(args), dtype_code(qkv.dtype), dtype_code(norm_dtype), _stream()),
            "rope_store")
 

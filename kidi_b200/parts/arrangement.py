@@ -19,11 +19,14 @@ get and return plain matrices.
 """
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, List
+
+import torch
 
 from ..errors import invalid_argument
 from .base import Part, ResidualSink, ResidualStream, plain_rows
 from .registry import register_part
+from .spec import ParamSpec
 
 
 import os
@@ -171,3 +174,86 @@ class SandwichNormBlock(Part):
         if self.feed_forward is not None:
             result = self.feed_forward.forward(plain_rows(self.post_norm.forward(stream)), ctx)
             stream.add(result, normed_by=self.feed_forward_out_norm)
+
+
+@register_part("arrangement", "hyper_connections")
+class HyperConnectionBlock(Part):
+    """A pre-norm block over a residual stream that is kept as `streams` lanes x_1 .. x_s (all equal to what the
+    embedding left, at the first such block). Sublayer q (1: the mixer, 2: the feed-forward, optional) reads one
+    weighted sum of the lanes and writes its result back into every lane while the lanes mix:
+
+        u = sum_s in_q[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y    (all t at once)
+
+    The sum that a norm reads is formed in the norm's kernel, the update of all lanes in one kernel; lanes, sums
+    and updates are 32-bit. After the last block the stream is the sum of the lanes (the norm before the head reads
+    that sum). Parameters: hidden_size, streams, and the tensor names under the prefix: in1, out1, mix1, in2, out2,
+    mix2 (defaults hc1.in, hc1.out, hc1.mix, hc2.in, hc2.out, hc2.mix)."""
+
+    ROLES = {"input_norm": "norm", "mixer": "mixer"}
+    OPTIONAL_ROLES = {"post_norm": "norm", "feed_forward": "feed_forward"}
+    MAX_STREAMS = 8
+
+    def __init__(self, spec, env, parts: Dict[str, Part]):
+        super().__init__(spec, env)
+        self.hidden = int(spec.param("hidden_size"))
+        self.streams = int(spec.param("streams"))
+        if not 1 <= self.streams <= self.MAX_STREAMS:
+            raise invalid_argument(f"a stream is kept as 1 to {self.MAX_STREAMS} lanes")
+        self.input_norm = parts["input_norm"]
+        self.mixer = parts["mixer"]
+        self.post_norm = parts.get("post_norm")
+        self.feed_forward = parts.get("feed_forward")
+        if (self.post_norm is None) != (self.feed_forward is None):
+            raise invalid_argument("a block has a feed-forward and the norm before it, or neither")
+        for norm in (self.input_norm, self.post_norm):
+            if norm is not None and not getattr(norm, "reads_lanes", False):
+                raise invalid_argument("the norms of a block over several lanes must be able to read lanes")
+        self.names = {key: spec.param(key + "_name", default) for key, default in (
+            ("in1", "hc1.in"), ("out1", "hc1.out"), ("mix1", "hc1.mix"), ("in2", "hc2.in"), ("out2", "hc2.out"),
+            ("mix2", "hc2.mix"))}
+        self.weights: Dict[str, torch.Tensor] = {}
+
+    def children(self):
+        return tuple(part for part in (self.input_norm, self.mixer, self.post_norm, self.feed_forward)
+                     if part is not None)
+
+    def parameter_specs(self) -> List[ParamSpec]:
+        count, n = self.streams, self.names
+        specs = []
+        for number in ("1", "2") if self.feed_forward is not None else ("1",):
+            specs += [ParamSpec(n["in" + number], (count,), init=("one_plus_normal", 0.2)),
+                      ParamSpec(n["out" + number], (count,), init=("one_plus_normal", 0.2)),
+                      ParamSpec(n["mix" + number], (count, count), init=("eye_plus_normal", 0.1))]
+        return specs
+
+    def bind(self, tensors) -> None:
+        self.weights = {key: tensors[name].float().contiguous() for key, name in self.names.items() if name in tensors}
+
+    def cache_requests(self) -> list:
+        return self.mixer.cache_requests()
+
+    def first_norm(self) -> Part:
+        return self.input_norm
+
+    def _write(self, stream: ResidualStream, number: str, result: torch.Tensor) -> None:
+        from ..kernels import ops
+        source = stream.lanes
+        if source.stride(0) == 0:        # still one matrix that stands for every lane: the lanes get memory now
+            stream.lanes = torch.empty(source.shape, dtype=torch.float32, device=source.device)
+        ops.lanes_mix(source, stream.lanes, self.weights["mix" + number], self.weights["out" + number],
+                      result.contiguous())
+
+    def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool) -> None:
+        if stream.lanes is None:
+            pending = stream.take_pending()
+            if pending is not None:
+                from ..kernels import ops
+                ops.add_cast(stream.hidden, pending, None)
+            stream.lanes = stream.hidden.unsqueeze(0).expand(self.streams, *stream.hidden.shape)
+        elif stream.lanes.shape[0] != self.streams:
+            raise invalid_argument("every block of a model keeps the stream as the same number of lanes")
+        normed = self.input_norm.forward(stream, read=self.weights["in1"])
+        self._write(stream, "1", self.mixer.forward(normed, ctx, views, owns_cache))
+        if self.feed_forward is not None:
+            normed = self.post_norm.forward(stream, read=self.weights["in2"])
+            self._write(stream, "2", self.feed_forward.forward(normed, ctx))

@@ -25,7 +25,17 @@ number per head, tensor `sink_name` [num_heads], whose exponential joins the sof
 (a key that every row sees, with that score as it is, unscaled, and no value); head_gate (bool):
 head h's result is multiplied by sigmoid(W_g x)_h, W_g the tensor `gate_name` [num_heads, hidden],
 its rows fused behind q, k and v into the one projection. Tensor names under the prefix are the
-parameters q_name, k_name, v_name, o_name, sink_name, gate_name.
+parameters q_name, k_name, v_name, o_name, sink_name, gate_name (and q_bias_name, k_bias_name, v_bias_name).
+
+Further parameters: output_gate (bool): the concatenated heads are multiplied element by element by
+sigmoid(W_g x), W_g the tensor `gate_name` [num_heads * value_dim, hidden], its rows fused into the one projection
+like a head gate's (a layer has one kind of gate or none); own_kv (default true; false: the layer has no key and
+value projections and reads, with its own queries, the keys and values that the layer named by the schedule
+entry's `cache_from` wrote: rotated keys as that layer's cache holds them); ring (default true; false: a
+windowed layer keeps every page and the window is a mask, so that prompts may continue cached sequences and
+another layer may read the cache); qk_norm_weight (default true; false: the per-head norm of q and k divides by
+the root mean square and has no weight); query_scale (name of a position part with a `table` of one factor per
+position: q is multiplied by its position's factor after norm and rotation).
 """
 from __future__ import annotations
 
@@ -63,9 +73,16 @@ class Attention(Part):
         self.value_dim = int(spec.param("value_dim", self.head_dim))
         self.has_sink = bool(spec.param("sink", False))
         self.has_gate = bool(spec.param("head_gate", False))
+        self.output_gate = bool(spec.param("output_gate", False))
+        self.own_kv = bool(spec.param("own_kv", True))
+        self.ring = bool(spec.param("ring", True))
+        self.norm_weight = bool(spec.param("qk_norm_weight", True))
+        if self.has_gate and self.output_gate:
+            raise invalid_argument("an attention layer has a gate per head or a gate per element, not both")
         self.names = {key: spec.param(key + "_name", default) for key, default in (
             ("q", "q_proj.weight"), ("k", "k_proj.weight"), ("v", "v_proj.weight"), ("o", "o_proj.weight"),
-            ("sink", "sinks"), ("gate", "gate_proj.weight"))}
+            ("sink", "sinks"), ("gate", "gate_proj.weight"), ("q_bias", "q_proj.bias"), ("k_bias", "k_proj.bias"),
+            ("v_bias", "v_proj.bias"))}
         scale = spec.param("scale", None)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(float(self.head_dim))
         if self.hidden <= 0 or self.heads <= 0 or self.kv_heads <= 0 or self.heads % self.kv_heads or self.head_dim <= 0:
@@ -84,7 +101,11 @@ class Attention(Part):
         self.out_width = self.heads * self.value_dim
         # The fused projection's rows: q, k, v, then one gate row a head, then zero rows up to a multiple of 8
         # (so that the rows of its result start on 16-byte boundaries).
-        self.fused_width = self.q_width + self.kv_width + self.v_width + (self.heads if self.has_gate else 0)
+        self.gate_width = self.heads if self.has_gate else self.out_width if self.output_gate else 0
+        self.gate_begin = self.q_width + (self.kv_width + self.v_width if self.own_kv else 0)
+        self.fused_width = self.gate_begin + self.gate_width
+        scale_name = spec.param("query_scale", None)
+        self.query_scale = env.positions[scale_name] if scale_name is not None else None
         self.sinks = None
         self.qkv: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -105,20 +126,22 @@ class Attention(Part):
 
     def parameter_specs(self) -> List[ParamSpec]:
         n = self.names
-        sources = [(n["q"], (self.q_width, self.hidden)), (n["k"], (self.kv_width, self.hidden)),
-                   (n["v"], (self.v_width, self.hidden))]
-        if self.has_gate:
-            sources.append((n["gate"], (self.heads, self.hidden)))
+        sources = [(n["q"], (self.q_width, self.hidden))]
+        biases = [(n["q_bias"], (self.q_width,))]
+        if self.own_kv:
+            sources += [(n["k"], (self.kv_width, self.hidden)), (n["v"], (self.v_width, self.hidden))]
+            biases += [(n["k_bias"], (self.kv_width,)), (n["v_bias"], (self.v_width,))]
+        if self.gate_width:
+            sources.append((n["gate"], (self.gate_width, self.hidden)))
         specs = [
             ParamSpec("qkv_proj.weight", (self.fused_width, self.hidden), sources=tuple(sources)),
             ParamSpec(n["o"], (self.hidden, self.out_width)),
         ]
         if self.qkv_bias:
-            specs.append(ParamSpec("qkv_proj.bias", (self.q_width + 2 * self.kv_width,), sources=(
-                ("q_proj.bias", (self.q_width,)), ("k_proj.bias", (self.kv_width,)), ("v_proj.bias", (self.kv_width,)))))
+            specs.append(ParamSpec("qkv_proj.bias", (self.gate_begin,), sources=tuple(biases)))
         if self.out_bias:
             specs.append(ParamSpec("o_proj.bias", (self.hidden,)))
-        if self.qk_norm:
+        if self.qk_norm and self.norm_weight:
             specs.append(ParamSpec("q_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
             specs.append(ParamSpec("k_norm.weight", (self.head_dim,), init=("one_plus_normal", 0.1)))
         if self.has_sink:
@@ -130,9 +153,15 @@ class Attention(Part):
         if self.fused_width % 8:
             pad = torch.zeros((8 - self.fused_width % 8, self.hidden), dtype=fused.dtype, device=fused.device)
             fused = torch.cat([fused, pad], dim=0).contiguous()
-        self.qkv = Linear(fused, tensors.get("qkv_proj.bias"))
+        bias = tensors.get("qkv_proj.bias")
+        if bias is not None and bias.shape[0] != fused.shape[0]:      # gate rows and padding rows carry no bias
+            bias = torch.cat([bias.float(), torch.zeros(fused.shape[0] - bias.shape[0], dtype=torch.float32,
+                                                        device=bias.device)])
+        self.qkv = Linear(fused, bias)
         self.out = Linear(tensors[self.names["o"]], tensors.get("o_proj.bias"))
-        if self.qk_norm:
+        if self.qk_norm and not self.norm_weight:
+            self.q_norm = self.k_norm = torch.ones(self.head_dim, dtype=torch.float32, device=fused.device)
+        elif self.qk_norm:
             self.q_norm, self.k_norm = tensors["q_norm.weight"], tensors["k_norm.weight"]
             if self.q_norm.dtype != self.k_norm.dtype:
                 self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
@@ -140,7 +169,8 @@ class Attention(Part):
             self.sinks = tensors[self.names["sink"]].float().contiguous()
 
     def cache_requests(self) -> list:
-        return [KVRequest(self.kv_heads, self.head_dim, int(self.window) if self.window is not None else None,
+        window = int(self.window) if self.window is not None and self.ring else None
+        return [KVRequest(self.kv_heads, self.head_dim, window,
                           value_dim=self.value_dim if self.value_dim != self.head_dim else None)]
 
     def launch_signature(self, rows: int, longest: int) -> tuple:
@@ -151,18 +181,23 @@ class Attention(Part):
     def forward(self, x, ctx, views, owns_cache: bool, sink=None) -> Optional[torch.Tensor]:
         view = views[0]
         plan = ctx.plan
+        if owns_cache and not self.own_kv:
+            raise invalid_argument("an attention layer without key and value projections reads another layer's cache "
+                                   "(the schedule entry's `cache_from`)")
         qkv = self.qkv.forward(x)
         position = self.position
         rotate = dict(cos=position.cos, sin=position.sin, rotary_dim=position.rotary_dim) if position is not None \
             else dict(cos=None, sin=None, rotary_dim=0)
-        common = dict(heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim, value_dim=self.value_dim)
+        if self.query_scale is not None:
+            rotate["q_scale"] = self.query_scale.table
+        common = dict(heads=self.heads, kv_heads=self.kv_heads if self.own_kv else 0, head_dim=self.head_dim,
+                      value_dim=self.value_dim)
         ring = view.ring_pages > 0
         extras = {}
         if self.has_sink:
             extras["sinks"] = self.sinks
         if self.has_gate:
-            begin = self.q_width + self.kv_width + self.v_width
-            extras["gate"] = qkv[:, begin:begin + self.heads]
+            extras["gate"] = qkv[:, self.gate_begin:self.gate_begin + self.heads]
         if self.value_dim != self.head_dim:
             extras["value_dim"] = self.value_dim
         # A ring that is written before attention would lose keys that the step's
@@ -173,8 +208,8 @@ class Attention(Part):
             raise unsupported("a layer that reads another layer's windowed cache takes one token per step")
         # One token per sequence on the tensor-core path: the attention kernel takes the rows as
         # the projection left them and does norm, rotation and the cache write itself.
-        fused = owns_cache and store_first and self.value_dim == self.head_dim and self.launcher.fuses_rotation(
-            plan, qkv, kv_view=view, q_norm=self.q_norm, k_norm=self.k_norm, **rotate)
+        fused = owns_cache and store_first and self.value_dim == self.head_dim and self.query_scale is None \
+            and self.launcher.fuses_rotation(plan, qkv, kv_view=view, q_norm=self.q_norm, k_norm=self.k_norm, **rotate)
         if not fused:
             ops.rope_store(qkv, q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, tables=ctx.tables, kv_view=view,
                            store=store_first, **rotate, **common)
@@ -182,8 +217,10 @@ class Attention(Part):
         keys_in_step = owns_cache and not plan.is_decode
         rotation = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps, store=True, **rotate) if fused else None
         self.launcher.run(ctx, qkv, attended, kv_view=view, keys_in_step=keys_in_step, rotation=rotation,
-                          step_rows_cached=store_first and not fused, **extras)
+                          step_rows_cached=store_first and not fused, q_only=not self.own_kv, **extras)
         if owns_cache and not store_first:
             ops.rope_store(qkv, q_norm=None, k_norm=None, eps=self.eps, tables=ctx.tables, kv_view=view, store=True,
                            transform=False, cos=None, sin=None, rotary_dim=0, **common)
+        if self.output_gate:
+            ops.sigmoid_gate(attended, qkv[:, self.gate_begin:self.gate_begin + self.out_width])
         return self.out.forward(attended, sink=sink)

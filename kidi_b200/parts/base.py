@@ -163,6 +163,10 @@ class ResidualStream:
         # float32, and how many of them are filled. `hidden` is then a view of one of them.
         self.kept: Optional[torch.Tensor] = None
         self.kept_count = 0
+        # A stream that layers keep as several lanes (float32 [count, rows, hidden]; see the `hyper_connections`
+        # arrangement): once set, the lanes are the stream, `hidden` is no longer kept up to date, and a norm reads a
+        # weighted sum of the lanes (their plain sum, for the norm before the head).
+        self.lanes: Optional[torch.Tensor] = None
 
     def add(self, delta: Optional[torch.Tensor], normed_by=None) -> None:
         """`delta` None: the part that made it has added it through a sink already. `normed_by`: a norm part

@@ -90,9 +90,10 @@ class DenseFeedForward(Part):
     under the prefix). Activations:
 
     * "poly_norm": a N(z) + b N(z^2) + c N(z^3) + e, powers element by element, N(u) = u / sqrt(mean(u^2) + eps)
-      over the intermediate values of a token, and (a, b, c, e) a tensor of four numbers."""
+      over the intermediate values of a token, and (a, b, c, e) a tensor of four numbers;
+    * "relu_squared": max(z, 0)^2 (no tensor of its own)."""
 
-    ACTIVATIONS = ("poly_norm",)
+    ACTIVATIONS = ("poly_norm", "relu_squared")
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -111,15 +112,20 @@ class DenseFeedForward(Part):
         self.coefficients: Optional[torch.Tensor] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(self.up_name, (self.inter, self.hidden)),
-                ParamSpec(self.down_name, (self.hidden, self.inter)),
-                ParamSpec(self.act_name, (4,), init=("normal", 0.5))]
+        specs = [ParamSpec(self.up_name, (self.inter, self.hidden)),
+                 ParamSpec(self.down_name, (self.hidden, self.inter))]
+        if self.activation == "poly_norm":
+            specs.append(ParamSpec(self.act_name, (4,), init=("normal", 0.5)))
+        return specs
 
     def bind(self, tensors) -> None:
         self.up = Linear(tensors[self.up_name])
         self.down = Linear(tensors[self.down_name])
-        self.coefficients = tensors[self.act_name].float().contiguous()
+        if self.activation == "poly_norm":
+            self.coefficients = tensors[self.act_name].float().contiguous()
 
     def forward(self, x, ctx, sink=None) -> Optional[torch.Tensor]:
         z = self.up.forward(x)
+        if self.activation == "relu_squared":
+            return self.down.forward(ops.relu_squared(z, out=z))
         return self.down.forward(ops.poly_norm(z, self.coefficients, self.eps))

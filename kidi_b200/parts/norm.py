@@ -45,13 +45,22 @@ class RMSNorm(Part):
         None when this norm does not take prepared rows."""
         return self.weight if self.env.dtype == torch.bfloat16 and not self.offset else None
 
+    reads_lanes = True            # a stream kept as several lanes is read as a weighted sum of them
+
     def forward(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, scaled: bool = False,
-                out_dtype: Optional[torch.dtype] = None):
+                out_dtype: Optional[torch.dtype] = None, read: Optional[torch.Tensor] = None):
         """Adds the stream's pending delta and returns the normalised rows in the
         engine dtype (or `out_dtype`). With `rows` (int32 indices) only those rows are produced and the
         stream itself is left untouched. With `scaled` the caller takes a `RowScaled` too:
         when the product before has prepared the rows (added its result to the stream, multiplied
-        by this norm's weight, summed the squares) there is nothing left to launch."""
+        by this norm's weight, summed the squares) there is nothing left to launch. A stream that is kept as
+        several lanes is read as sum_s read[s] * lane_s (`read` float32 [lanes]; None: the plain sum) and
+        normalised in the same kernel."""
+        if stream.lanes is not None:
+            if self.offset and self.weight.dtype != torch.float32:
+                raise RuntimeError("a norm with a weight offset keeps its weight in 32-bit")
+            return ops.lanes_rmsnorm(stream.lanes, read, self.weight, self.eps, out_dtype or self.env.dtype,
+                                     row_index=rows)
         prepared = stream.take_prepared(self) if rows is None else None
         if prepared is not None:
             ready = RowScaled(prepared[0], prepared[1], self.size, self.eps)

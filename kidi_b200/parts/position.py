@@ -18,6 +18,10 @@ and cosine and sine are both multiplied by 0.1 ln(factor) + 1.
 (times `scale`, default 1), in 32-bit; mixers read nothing from it. Parameters: hidden_size,
 max_positions, scale, name (the table's tensor name under the prefix, default "weight").
 
+`query_temperature` is a factor per position that an attention layer multiplies its queries by (named in the
+layer's `query_scale`): 1 + coef * ln(floor((p + 1) / every) + 1) at position p, so that scores sharpen step by
+step as a sequence grows. Parameters: coef, every, max_positions. The table is 32-bit, built once.
+
 Interface of a position encoding: `on_embeddings(stream, ctx)` (may change the
 embeddings; rotary does nothing there) and whatever its mixers agree to read from it
 (`cos`, `sin`, `rotary_dim` here).
@@ -109,3 +113,27 @@ class LearnedPositions(Part):
 
     def on_embeddings(self, stream, ctx) -> None:
         ops.add_table_rows(stream.hidden, self.table, ctx.tables.row_pos, self.scale)
+
+
+@register_part("position", "query_temperature")
+class QueryTemperature(Part):
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.coef = float(spec.param("coef"))
+        self.every = int(spec.param("every"))
+        self.max_positions = int(spec.param("max_positions"))
+        if self.every <= 0 or self.max_positions <= 0:
+            raise invalid_argument("a query temperature needs a positive interval and length")
+        self._table = None
+
+    @property
+    def table(self) -> torch.Tensor:
+        """float32 [max_positions] on the device: the factor of each position (computed in 64-bit, rounded once)."""
+        if self._table is None:
+            position = torch.arange(self.max_positions, dtype=torch.float64)
+            factor = 1.0 + self.coef * torch.log(torch.floor((position + 1.0) / self.every) + 1.0)
+            self._table = factor.float().contiguous().to(self.env.device)
+        return self._table
+
+    def on_embeddings(self, stream, ctx) -> None:
+        return None

@@ -142,7 +142,7 @@ class ParamSpec:
     pairs concatenated on axis 0 in order, which is the reference's q/k/v -> qkv and
     gate/up -> gate_up rule (src/kidi/model/qwen3.cpp:113-132).
     `init` names the random-weights distribution: ("normal", std), ("one_plus_normal", std),
-    ("uniform", high) on [0, high) or ("last_one", std): N(0, std) with 1 added to the last entry. `storage` is "float" (bfloat16, or 32-bit when the
+    ("uniform", high) on [0, high), ("eye_plus_normal", std): the identity plus N(0, std), or ("last_one", std): N(0, std) with 1 added to the last entry. `storage` is "float" (bfloat16, or 32-bit when the
     file stores 32-bit) or "int32".
     """
 

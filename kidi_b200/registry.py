@@ -93,3 +93,4 @@ def _load_builtin() -> None:
         from .models import sanozen  # noqa: F401
         from .models import gakenex  # noqa: F401
         from .models import gazezen  # noqa: F401
+        from .models import biropel  # noqa: F401

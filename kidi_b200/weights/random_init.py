@@ -41,6 +41,8 @@ def _draw(name: str, shape: Tuple[int, ...], init: Tuple[str, float], seed: int,
         values.mul_(std).add_(1.0)
     elif kind == "uniform":
         values = torch.rand(shape, generator=generator, dtype=torch.float32, device=device) * std
+    elif kind == "eye_plus_normal":       # a square matrix near the identity
+        values.mul_(std).add_(torch.eye(shape[0], shape[1], dtype=torch.float32, device=device))
     elif kind == "last_one":
         values.mul_(std)
         values.reshape(-1)[-1] += 1.0
