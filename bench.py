@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--model 8b|14b|32b] [--impl ours|reference]
-    python bench.py --design sanozen|gakenex|gazezen [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
+    python bench.py --design sanozen|gakenex|gazezen|biropel [--widths 2048,4096] [--layers 4]     (another record; see `design_comparison`)
 
 A step is one decode step of the batch. The default run is the Qwen3-8B shape (every
 layer size, all 36 layers) with random bfloat16 weights drawn on the device from a
@@ -350,7 +350,41 @@ def gazezen_shape(width: int, layers: int = 4) -> dict:
             "logit_scale": 0.7, "layers": stack}
 
 
-DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape, "gazezen": gazezen_shape}
+def biropel_shape(width: int, layers: int = 4) -> dict:
+    """A Biropel stack at the layer sizes of a model of `width`, its kinds of layer in turn: an attention layer
+    (heads of 128, a key/value head for four heads, half of a head rotated, a window of 4,096, biases, an element-wise
+    gate), an attention layer that reads the keys and values of the one before it, attention with stretched
+    frequencies and bounded scores (half the heads) beside a state-space mixer (heads of 64 values, inner width =
+    width, a state of 128 rows, four taps), and attention with normalised queries and keys, a query temperature and
+    bounded scores (half the heads, every earlier token visible) beside a matrix memory (heads of 128 x 128, half the
+    heads). Squared-relu feed-forwards of 4 width (as many weights as the Qwen3 layers' gated ones); two lanes."""
+    heads = width // 128
+    groups = max(1, heads // 4)
+    half, half_groups = max(1, heads // 2), max(1, heads // 8)
+    mlp = {"kind": "dense", "ff": 4 * width}
+    base = {"heads": heads, "kv_heads": groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 4096},
+            "rot": {"base": 1000000.0, "dims": 64}}
+    stretched = {"heads": half, "kv_heads": half_groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "mask": {"size": 4096}, "softcap": 30.0, "rot": {"base": 500000.0, "dims": 128, "scaling": {
+                     "factor": 8.0, "original": 1024.0, "fast": 32.0, "slow": 1.0}}}
+    unrotated = {"heads": half, "kv_heads": half_groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                 "q_temp": {"coef": 0.1, "every": 1024}}
+    kinds = [
+        lambda: {"type": "attention", "mixer": dict(base), "mlp": dict(mlp)},
+        lambda source: {"type": "attention", "mixer": dict(base, kv_from=source), "mlp": dict(mlp)},
+        lambda: {"type": "parallel", "mixer": {"left": dict(stretched), "right": {
+            "heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 8}}, "mlp": dict(mlp)},
+        lambda: {"type": "parallel_2", "mixer": {"left": dict(unrotated), "right": {
+            "heads": half, "dim": 128, "vdim": 128, "gate_cap": 15.0}}, "mlp": dict(mlp)},
+    ]
+    stack = []
+    for index in range(layers):
+        stack.append(kinds[1](index - 1) if index % 4 == 1 else kinds[index % 4]())
+    return {"architecture": "Biropel", "vocab": 32768, "width": width, "max_positions": 8192, "norm": {"eps": 1e-5},
+            "streams": 2, "layers": stack}
+
+
+DESIGN_SHAPES = {"sanozen": sanozen_shape, "gakenex": gakenex_shape, "gazezen": gazezen_shape, "biropel": biropel_shape}
 
 
 def qwen3_shape(width: int, layers: int = 4) -> dict:
@@ -366,15 +400,15 @@ KERNEL_CLASSES = (
     ("products", ("gemm_", "library_mm", "library_bmm", "gemm_heads")),
     ("prompt attention", ("attention_prefill",)),
     ("decode attention", ("attention_decode", "latent_attention")),
-    ("recurrence", ("gated_recurrence",)),
-    ("stream norm", ("add_rmsnorm", "add_layernorm")),
-    ("activation", ("silu_gate", "poly_norm", "bounded_gate", "gelu")),
+    ("recurrence", ("gated_recurrence", "scalar_recurrence")),
+    ("stream norm", ("add_rmsnorm", "add_layernorm", "lanes_")),
+    ("activation", ("silu_gate", "poly_norm", "bounded_gate", "gelu", "relu_squared")),
     ("experts through the choice", ("expert_slots",)),
 )
 
 
 def kernel_class(name: str, decode: bool = False) -> str:
-    if name.startswith("diff_attention"):
+    if name.startswith("diff_attention") or name == "attention":      # (`attention`: the general kernel)
         return "decode attention" if decode else "prompt attention"
     for label, prefixes in KERNEL_CLASSES:
         if name.startswith(prefixes):
@@ -469,6 +503,41 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
         work["decode attention"] = ("bytes", cache)
         if decode:
             work["experts through the choice"] = ("bytes", chosen)
+    elif design == "biropel":
+        width, layers, lanes = config["width"], config["layers"], config.get("streams") or 1
+        weights, norms, act_width, attention, cache, scan, stream = config["vocab"] * width, 0, 0, 0.0, 0.0, 0.0, 0.0
+        sequences = rows if decode else 1
+        for layer in layers:
+            ff = layer["mlp"]["ff"] if layer["mlp"] else 0
+            weights += 2 * width * ff
+            act_width += 2 * ff                                      # read and written
+            sublayers = 2 if ff else 1
+            # a norm reads every lane and writes bfloat16 rows; an update reads the lanes and the result, writes the lanes
+            stream += sublayers * rows * width * ((4 * lanes + 2) + (8 * lanes + 4.0))
+            left = layer["mixer"] if layer["type"] == "attention" else layer["mixer"]["left"]
+            heads, groups, dim, vdim = left["heads"], left["kv_heads"], left["dim"], left["vdim"]
+            own = 0 if "kv_from" in left else groups * (dim + vdim)
+            gate = heads * vdim if layer["type"] == "attention" else 0
+            weights += width * (heads * dim + own + gate) + heads * vdim * width
+            attention += 2.0 * heads * (dim + vdim) * rows * (rows + 1) / 2
+            reach = min(context, left["mask"]["size"]) if "mask" in left else context
+            cache += rows * reach * groups * (dim + vdim) * 2.0
+            right = layer["mixer"].get("right")
+            if layer["type"] == "parallel":
+                inner, span = right["heads"] * right["vdim"], right["groups"] * right["state"]
+                weights += width * (2 * inner + 2 * span + right["heads"]) + inner * width
+                scan += rows * (inner + 2 * span) * 2.0 + rows * inner * 4.0 \
+                    + sequences * 2.0 * right["heads"] * right["state"] * right["vdim"] * 4
+            elif layer["type"] == "parallel_2":
+                keys, values = right["heads"] * right["dim"], right["heads"] * right["vdim"]
+                weights += width * (2 * keys + 2 * values + 2 * right["heads"]) + values * width
+                scan += rows * (2 * keys + values) * 2.0 + rows * (values + right["heads"]) * 4.0 \
+                    + sequences * 2.0 * right["heads"] * right["dim"] * (right["vdim"] + 1) * 4
+        work["prompt attention"] = ("flops", attention)
+        work["decode attention"] = ("bytes", cache)
+        work["recurrence"] = ("bytes", scan)
+        norms = 2                                                     # the embedding's norm and the final one
+        stream += 0.0
     else:
         width, layers = config["width"], config["layers"]
         weights, norms, act_width, attention, cache, scan_flops, scan_bytes, state = config["vocab"] * width, 1, 0, 0.0, 0.0, 0.0, 0.0, 0.0
@@ -492,7 +561,7 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
         work["decode attention"] = ("bytes", cache)
         work["recurrence"] = ("bytes", scan_bytes + (rows if decode else 1) * state)
     work["products"] = ("bytes", 2.0 * weights) if decode else ("flops", 2.0 * rows * weights)
-    work["stream norm"] = ("bytes", norms * rows * width * (4 + 4 + 2 + 2.0))
+    work["stream norm"] = ("bytes", norms * rows * width * (4 + 4 + 2 + 2.0) + (stream if design == "biropel" else 0.0))
     work["activation"] = ("bytes", rows * act_width * 2.0)
     if decode:
         work.pop("prompt attention")
@@ -502,7 +571,7 @@ def class_work(design: str, config: dict, rows: int, context: int, decode: bool)
 
 
 def design_comparison(args) -> int:
-    """`--design sanozen` / `--design gakenex` / `--design gazezen`: prompts and decoding of a stack of that design beside Qwen3 layers
+    """`--design sanozen` / `--design gakenex` / `--design gazezen` / `--design biropel`: prompts and decoding of a stack of that design beside Qwen3 layers
     of equal size, with every class of kernel against its roofline."""
     import torch
     from kidi_b200 import Engine
@@ -564,7 +633,7 @@ def design_comparison(args) -> int:
 
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    parser.add_argument("--design", default="", choices=["", "sanozen", "gakenex", "gazezen"],
+    parser.add_argument("--design", default="", choices=["", "sanozen", "gakenex", "gazezen", "biropel"],
                         help="a Sanozen, Gakenex or Gazezen stack beside Qwen3 layers of equal size, kernel class by kernel class "
                              "(the default workload is left as it is)")
     parser.add_argument("--widths", default="2048,4096", help="model widths of --design runs")

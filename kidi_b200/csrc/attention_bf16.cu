@@ -141,7 +141,35 @@ struct Args {
                               // row sees, with that score as it is, unscaled, and no value)
     const bf16* gate;         // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
     long long ldg;
+    float softcap;            // > 0: a scaled score s becomes softcap * tanh(s / softcap)
 };
+
+// How a raw dot product becomes a score in base-2 exponent units: times scale * log2(e), or, bounded,
+// softcap * log2(e) * tanh(raw * scale / softcap).
+struct ScoreShape {
+    float scale_log2, inner, outer;     // outer > 0: the bounded form, outer * tanh(raw * inner)
+};
+
+__device__ __forceinline__ ScoreShape score_shape(float scale, float softcap) {
+    ScoreShape shape;
+    shape.scale_log2 = scale * LOG2E;
+    shape.inner = softcap > 0.f ? scale / softcap : 0.f;
+    shape.outer = softcap > 0.f ? softcap * LOG2E : 0.f;
+    return shape;
+}
+
+// tanh as 1 - 2 / (exp(2x) + 1): a few units in the last place of 1 (the hardware's tanh.approx is good to
+// 2^-11 only, which a bound of 30 would turn into a hundredth of a score).
+__device__ __forceinline__ float tanh_near(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    float power;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(power) : "f"(x * (2.f * LOG2E)));
+    return 1.f - __fdividef(2.f, power + 1.f);
+}
+
+__device__ __forceinline__ float shaped(float raw, const ScoreShape& shape) {
+    return shape.outer > 0.f ? shape.outer * tanh_near(raw * shape.inner) : raw * shape.scale_log2;
+}
 
 // What the weighted sum of a finished (row, head) is multiplied by: 1 / (denominator, with the head's sink in
 // it), times the row's gate. `top` is the maximum that the denominator `total` is relative to, in log2 units.
@@ -241,10 +269,10 @@ __device__ __forceinline__ void softmax_and_weighted_sum(float (&s)[NT][4], floa
 }
 
 // Scores of one warp: 16 query rows (A from q_tile rows [q_row, q_row+16)) against
-// NT*8 keys starting at `first_key` of k_tile, times scale_log2.
+// NT*8 keys starting at `first_key` of k_tile, as scores in base-2 exponent units.
 template <int NT>
 __device__ __forceinline__ void scores(float (&s)[NT][4], const bf16* q_tile, int q_row, const bf16* k_tile,
-                                       int first_key, float scale_log2, int lane) {
+                                       int first_key, const ScoreShape& shape, int lane) {
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
@@ -265,7 +293,7 @@ __device__ __forceinline__ void scores(float (&s)[NT][4], const bf16* q_tile, in
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) s[j][i] *= scale_log2;
+        for (int i = 0; i < 4; ++i) s[j][i] = shaped(s[j][i], shape);
 }
 
 // ------------------------------------------------------------------- prefill
@@ -305,7 +333,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
     for (int n = 0; n < D / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-    const float scale_log2 = a.scale * LOG2E;
+    const ScoreShape shape = score_shape(a.scale, a.softcap);
     const int position0 = start + q0 + warp * 16 + g;       // query position of accumulator rows 0,1 (and +8 for 2,3)
 
     for (int tile = tile_low; tile <= tile_high; ++tile) {
@@ -325,7 +353,7 @@ __global__ void __launch_bounds__(THREADS) attention_prefill_kernel(Args a) {
         const bool active = warp * 16 < q_rows && start + q0 + warp * 16 + 15 >= tile * TILE;
         if (active) {
             float s[8][4];
-            scores<8>(s, q_tile, warp * 16, k_tiles + buffer * TILE * PITCH, 0, scale_log2, lane);
+            scores<8>(s, q_tile, warp * 16, k_tiles + buffer * TILE * PITCH, 0, shape, lane);
 #pragma unroll
             for (int j = 0; j < 8; ++j)
 #pragma unroll
@@ -409,7 +437,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
         load_tile(k_tiles, nullptr, 0, 0, 0x7fffffff, a.k_cache, a.cache, slot, kv_head, tile_first, position);
         load_tile(v_tiles, nullptr, 0, 0, 0x7fffffff, a.v_cache, a.cache, slot, kv_head, tile_first, position);
         copy_async_commit();
-        const float scale_log2 = a.scale * LOG2E;
+        const ScoreShape shape = score_shape(a.scale, a.softcap);
         for (int index = 0; index < tiles; ++index) {
             const int tile = tile_first + index, buffer = index & 1;
             if (index + 1 < tiles) {
@@ -426,7 +454,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(Args a) {
             const int first_key = warp * 16;
             if (tile * TILE + first_key <= position && tile * TILE + first_key + 15 >= low) {
                 float s[2][4];
-                scores<2>(s, q_tile, 0, k_tiles + buffer * TILE * PITCH, first_key, scale_log2, lane);
+                scores<2>(s, q_tile, 0, k_tiles + buffer * TILE * PITCH, first_key, shape, lane);
 #pragma unroll
                 for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -775,7 +803,7 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
             copy_async_16(q_tile + r * PITCH + c * 8, source, valid);
         }
         copy_async_commit();
-        const float scale_log2 = a.scale * LOG2E;
+        const ScoreShape shape = score_shape(a.scale, a.softcap);
         unsigned q_frag[D / 16][2];                         // Q^T as B operand: (dims, head g)
         for (int index = 0; index < tiles; ++index) {
             const int tile = tile_first + index, buffer = index & 1;
@@ -865,10 +893,10 @@ attention_decode_narrow_kernel(const __grid_constant__ CUtensorMap k_map, const 
                 }
                 const int u0 = tile * TILE + first_key + g, u1 = u0 + 8;
                 const bool see0 = u0 <= position && u0 >= low, see1 = u1 <= position && u1 >= low;
-                s[0] = see0 ? s[0] * scale_log2 : -INFINITY;
-                s[1] = see0 ? s[1] * scale_log2 : -INFINITY;
-                s[2] = see1 ? s[2] * scale_log2 : -INFINITY;
-                s[3] = see1 ? s[3] * scale_log2 : -INFINITY;
+                s[0] = see0 ? shaped(s[0], shape) : -INFINITY;
+                s[1] = see0 ? shaped(s[1], shape) : -INFINITY;
+                s[2] = see1 ? shaped(s[2], shape) : -INFINITY;
+                s[3] = see1 ? shaped(s[3], shape) : -INFINITY;
                 float top[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
 #pragma unroll
                 for (int i = 0; i < 2; ++i) {               // over the eight lanes that share t

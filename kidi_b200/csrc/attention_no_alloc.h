@@ -83,6 +83,7 @@ struct KidiAttentionArgs {
     const float* sinks;            // [heads] float32 or null: exp(sinks[h]) joins head h's softmax denominator
     const void* gate;              // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
     long long ldg;
+    float softcap;                 // > 0: a scaled score s becomes softcap * tanh(s / softcap); 0: scores as they are
 };
 
 // Bounds the static entry point checks before it forms the size of the workspace.

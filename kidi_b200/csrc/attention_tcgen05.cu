@@ -226,6 +226,7 @@ struct Params {
                             // row sees, with that score as it is, unscaled, and no value)
     const bf16* gate;       // [rows, ldg] or null: head h of a row is multiplied by sigmoid(gate[row, h])
     long long ldg;
+    float softcap;          // > 0: a scaled score s becomes softcap * tanh(s / softcap)
 };
 
 // Where a block works: its sequence, query rows, heads and key tiles.
@@ -253,6 +254,13 @@ struct Place {
         tiles = high / BN - tile_low + 1;
     }
 };
+
+// tanh as 1 - 2 / (exp(2x) + 1): a few units in the last place of 1 (the hardware's tanh.approx is good to
+// 2^-11 only, which a bound of 30 would turn into a hundredth of a score).
+__device__ __forceinline__ float tanh_near(float x) {
+    x = fminf(fmaxf(x, -15.f), 15.f);
+    return 1.f - __fdividef(2.f, exp2_approx(x * (2.f * LOG2E)) + 1.f);
+}
 
 // One softmax thread holds SHARE raw scores of a query row: the keys first..last (relative
 // to the thread's first key) are the ones the row may see. Returns their maximum, scaled
@@ -507,6 +515,11 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map, const 
                 tmem_load_wait();
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 mbarrier_arrive(&ctl.s_free[h]);
+                if (p.softcap > 0.f) {      // bounded scores: the raw scores take the form that `scale` then restores
+                    const float inner = p.scale / p.softcap, outer = p.softcap / p.scale;
+#pragma unroll
+                    for (int i = 0; i < SHARE; ++i) s[i] = outer * tanh_near(s[i] * inner);
+                }
                 const float mine = masked ? share_maximum<true>(s, scale_log2, first, last)
                                           : share_maximum<false>(s, scale_log2, first, last);
                 Exchange(&parts)[GROUPS] = ctl.row_part[h][exchanges & 1][r];
@@ -661,6 +674,7 @@ struct KidiHeadExtras {      // what a head's result passes beside the plain sof
     const float* sinks;      // [heads] float32: exp(sinks[h]) joins head h's softmax denominator
     const void* gate;        // [rows, ldg] bfloat16: head h of a row is multiplied by sigmoid(gate[row, h])
     long long ldg;
+    float softcap;           // > 0: a scaled score s becomes softcap * tanh(s / softcap)
 };
 
 // `cache` null: every sequence starts at position 0 and its keys are rows of qkv. Else every
@@ -735,6 +749,7 @@ KIDI_API int kidi_attention_prefill_tcgen05(const void* qkv, long long ld, int r
         p.sinks = extras->sinks;
         p.gate = (const bf16*)extras->gate;
         p.ldg = extras->ldg;
+        p.softcap = extras->softcap;
     }
     const int group_size = heads / kv_heads;
     dim3 grid(kv_heads * ((group_size + HEADS - 1) / HEADS), seqs, (max_new + BM - 1) / BM);

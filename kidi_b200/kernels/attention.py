@@ -45,7 +45,7 @@ class FastAttentionArgs(ctypes.Structure):
                 ("counters", c_void_p), ("fuse", c_int), ("norm_is_float", c_int), ("q_norm", c_void_p),
                 ("k_norm", c_void_p), ("cos_table", c_void_p), ("sin_table", c_void_p), ("rotary_dim", c_int),
                 ("eps", c_float), ("cache_rows", c_longlong), ("sinks", c_void_p), ("gate", c_void_p),
-                ("ldg", c_longlong)]
+                ("ldg", c_longlong), ("softcap", c_float)]
 
 
 _libraries: Dict[int, ctypes.CDLL] = {}
@@ -101,7 +101,7 @@ class PromptCache(ctypes.Structure):
 
 class HeadExtras(ctypes.Structure):
     """A number per head in the softmax denominator and a sigmoid gate per row and head (KidiHeadExtras)."""
-    _fields_ = [("sinks", c_void_p), ("gate", c_void_p), ("ldg", c_longlong)]
+    _fields_ = [("sinks", c_void_p), ("gate", c_void_p), ("ldg", c_longlong), ("softcap", c_float)]
 
 
 def extras_fit(sinks: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int) -> bool:
@@ -115,7 +115,7 @@ def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.T
                           seqs: int, max_new: int, *, heads: int, kv_heads: int, head_dim: int, scale: float,
                           window: int, kv_view=None, seq_start: Optional[torch.Tensor] = None,
                           seq_slot: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                          gate: Optional[torch.Tensor] = None, q_only: bool = False) -> None:
+                          gate: Optional[torch.Tensor] = None, q_only: bool = False, softcap: float = 0.0) -> None:
     """Causal attention of packed prompts. Without `kv_view` the prompts start at position 0
     and every key is a row of qkv; with it (a cache of 64-token pages without a ring, into
     which the step's rows have been written) every key and value is read from the cache,
@@ -123,9 +123,9 @@ def prefill_tensor_memory(qkv: torch.Tensor, out: torch.Tensor, seq_len: torch.T
     `kv_view`): the rows of qkv hold the query heads only."""
     lib = tensor_memory_library(head_dim)
     cache = extras = None
-    if sinks is not None or gate is not None:
+    if sinks is not None or gate is not None or softcap:
         extras = HeadExtras(sinks.data_ptr() if sinks is not None else 0, gate.data_ptr() if gate is not None else 0,
-                            gate.stride(0) if gate is not None else 0)
+                            gate.stride(0) if gate is not None else 0, float(softcap or 0.0))
     if kv_view is not None:
         cache = PromptCache(kv_view.keys.data_ptr(), kv_view.values.data_ptr(), kv_view.keys.numel() // head_dim,
                             kv_view.table.data_ptr(), kv_view.table.shape[1], seq_start.data_ptr(), seq_slot.data_ptr(),
@@ -258,9 +258,9 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
     query heads only (every key and value comes from the cache)."""
     plan, tables = ctx.plan, ctx.tables
     decode = plan.is_decode and not keys_in_step
-    # Scores that are bounded or shifted by position run on the general kernel (the tensor-core kernels
-    # compute plain scaled scores).
-    reshaped = bool(softcap) or slopes is not None
+    # Scores that are shifted by position run on the general kernel (the tensor-core kernels compute scaled
+    # scores, bounded by a tanh where a layer asks for it).
+    reshaped = slopes is not None
     uneven = value_dim is not None and value_dim != head_dim
     if (reshaped or uneven or not extras_fit(sinks, gate, heads)
             or not fast_fits(qkv.dtype, heads, kv_heads, head_dim, decode)
@@ -271,7 +271,7 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         return
     if not decode and tensor_memory_fits(qkv, out, head_dim, heads, kv_heads, scale):
         common = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, scale=scale, window=window, sinks=sinks,
-                      gate=gate)
+                      gate=gate, softcap=softcap)
         if keys_in_step and int(plan.seq_start.max()) == 0:      # every key is a row of this step
             prefill_tensor_memory(qkv, out, tables.seq_len, tables.seq_row0, plan.n_seqs, plan.max_new, **common)
             return
@@ -296,6 +296,7 @@ def run(ctx, qkv, out, *, heads, kv_heads, head_dim, scale, window, kv_view, key
         args.sinks = sinks.data_ptr()
     if gate is not None:
         args.gate, args.ldg = gate.data_ptr(), gate.stride(0)
+    args.softcap = float(softcap or 0.0)
     lib = library(head_dim)
     stream = ops._stream()
     if not decode:
@@ -362,10 +363,10 @@ class AttentionLauncher:
                  softcap: float = 0.0, slopes: Optional[torch.Tensor] = None):
         self.geometry = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim)
         self.scale, self.window = scale, window
-        # Scores bounded by softcap * tanh(s / softcap), or shifted by slopes[head] * (key - query position):
-        # such scores run on the general kernel.
+        # Scores bounded by softcap * tanh(s / softcap) run on every kernel; scores shifted by slopes[head] *
+        # (key - query position) run on the general kernel.
         self.softcap, self.slopes = float(softcap or 0.0), slopes
-        self.reshaped = bool(self.softcap) or slopes is not None
+        self.reshaped = slopes is not None
 
     def fuses_rotation(self, plan, qkv, **arguments) -> bool:
         """Whether `run` can do norm, rotation and the cache write of this step itself."""

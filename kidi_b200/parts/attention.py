@@ -16,8 +16,8 @@ its Linear has the option, src/kidi/layers/linear.cpp:181-190), score_softcap (a
 becomes cap * tanh(s / cap); default none) and score_slopes (one number per head: head h adds
 slope * (key position - query position) to its scores; default none). The last two have no
 counterpart in the reference's Qwen3; they are there so that an architecture that bounds or
-shifts its scores is a specification, not a change to the kernels' arguments: such layers run
-on the general attention kernel in either precision.
+shifts its scores is a specification, not a change to the kernels' arguments: every attention kernel takes the
+bound; layers with slopes run on the general attention kernel in either precision.
 
 Three more, none of them in the reference's Qwen3: value_dim (the width of a value head, default
 head_dim: the output projection then takes num_heads * value_dim columns); sink (bool): a learned
