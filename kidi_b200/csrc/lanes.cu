@@ -70,6 +70,96 @@ __global__ void lanes_mix_kernel(const float* source, long long source_stride, f
     }
 }
 
+// Four consecutive elements as 32-bit values (the address is aligned to four elements).
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const bf16* p, float (&v)[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(bf16* p, const float (&v)[4]) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same as lanes_rmsnorm_kernel for widths that are multiples of four and aligned rows: four elements a thread and
+// step, the loads of all lanes in flight together. The sums are formed in the same order.
+template <typename TW, typename TY>
+__global__ void __launch_bounds__(LANE_THREADS)
+lanes_rmsnorm_x4_kernel(const float* __restrict__ lanes, long long lane_stride, int count, const float* __restrict__ read,
+                        const TW* __restrict__ weight, TY* __restrict__ y, const int* __restrict__ row_index, int hidden,
+                        float eps) {
+    extern __shared__ __align__(16) float staged[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float square = 0.f;
+    for (int c = 4 * threadIdx.x; c < hidden; c += 4 * LANE_THREADS) {
+        float sum[4];
+        for (int l = 0; l < count; ++l) {
+            float value[4];
+            load4(lanes + l * lane_stride + s * hidden + c, value);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                sum[i] = l == 0 ? (read ? read[0] * value[i] : value[i])
+                                : (read ? fmaf(read[l], value[i], sum[i]) : sum[i] + value[i]);
+        }
+        store4(staged + c, sum);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) square = fmaf(sum[i], sum[i], square);
+    }
+    float inv = 1.f;
+    if (weight) inv = 1.0f / sqrtf(block_sum<LANE_THREADS>(square, scratch) / (float)hidden + eps);
+    for (int c = 4 * threadIdx.x; c < hidden; c += 4 * LANE_THREADS) {
+        float value[4], w[4];
+        load4(staged + c, value);
+        if (weight) {
+            load4(weight + c, w);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) value[i] = value[i] * inv * w[i];
+        }
+        store4(y + (long long)r * hidden + c, value);
+    }
+}
+
+// lanes_mix_kernel, four elements a thread.
+template <typename TY>
+__global__ void lanes_mix_x4_kernel(const float* source, long long source_stride, float* target, long long target_stride,
+                                    int count, const float* __restrict__ mix, const float* __restrict__ write,
+                                    const TY* __restrict__ y, long long groups) {
+    const long long index = 4 * ((long long)blockIdx.x * blockDim.x + threadIdx.x);
+    if (index >= 4 * groups) return;
+    float old[MAX_LANES][4], delta[4];
+#pragma unroll
+    for (int l = 0; l < MAX_LANES; ++l)
+        if (l < count) load4(source + l * source_stride + index, old[l]);
+    load4(y + index, delta);
+#pragma unroll
+    for (int t = 0; t < MAX_LANES; ++t) {
+        if (t >= count) break;
+        float sum[4];
+#pragma unroll
+        for (int l = 0; l < MAX_LANES; ++l)
+            if (l < count) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    sum[i] = l == 0 ? mix[t] * old[0][i] : fmaf(mix[l * count + t], old[l][i], sum[i]);
+            }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum[i] = fmaf(write[t], delta[i], sum[i]);
+        store4(target + t * target_stride + index, sum);
+    }
+}
+
 // One block per row: both rows staged, their mean squares, then the weighted sum of the two normalised rows.
 template <typename T, typename TY>
 __global__ void __launch_bounds__(LANE_THREADS)
@@ -134,14 +224,16 @@ template <typename TW>
 int lanes_rmsnorm_out(const float* lanes, long long lane_stride, int count, const float* read, const TW* weight, void* y,
                       int y_dtype, const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
     const size_t shared = (size_t)hidden * sizeof(float);
+    const bool x4 = hidden % 4 == 0 && lane_stride % 4 == 0 && !((uintptr_t)lanes & 15) && !((uintptr_t)weight & 15) &&
+                    !((uintptr_t)y & 15);
     if (y_dtype == KIDI_F32) {
-        auto kernel = lanes_rmsnorm_kernel<TW, float>;
+        auto kernel = x4 ? lanes_rmsnorm_x4_kernel<TW, float> : lanes_rmsnorm_kernel<TW, float>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, lanes, lane_stride, count, read, weight, (float*)y,
                            row_index, hidden, eps);
     }
     if (y_dtype == KIDI_BF16) {
-        auto kernel = lanes_rmsnorm_kernel<TW, bf16>;
+        auto kernel = x4 ? lanes_rmsnorm_x4_kernel<TW, bf16> : lanes_rmsnorm_kernel<TW, bf16>;
         if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, lanes, lane_stride, count, read, weight, (bf16*)y,
                            row_index, hidden, eps);
@@ -188,6 +280,18 @@ KIDI_API int kidi_lanes_mix(const float* source, long long source_stride, float*
                             long long total, cudaStream_t stream) {
     if (total <= 0) return 0;
     if (count <= 0 || count > MAX_LANES) return KIDI_REFUSED_SIZE;
+    if (total % 4 == 0 && source_stride % 4 == 0 && target_stride % 4 == 0 && !((uintptr_t)source & 15) &&
+        !((uintptr_t)target & 15) && !((uintptr_t)y & 15)) {
+        const long long groups = total / 4;
+        const unsigned vector_blocks = (unsigned)((groups + 255) / 256);
+        if (y_dtype == KIDI_F32)
+            return kidi_launch(lanes_mix_x4_kernel<float>, vector_blocks, 256, 0, stream, source, source_stride, target,
+                               target_stride, count, mix, write, (const float*)y, groups);
+        if (y_dtype == KIDI_BF16)
+            return kidi_launch(lanes_mix_x4_kernel<bf16>, vector_blocks, 256, 0, stream, source, source_stride, target,
+                               target_stride, count, mix, write, (const bf16*)y, groups);
+        return KIDI_REFUSED_DTYPE;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (y_dtype == KIDI_F32)
         return kidi_launch(lanes_mix_kernel<float>, blocks, 256, 0, stream, source, source_stride, target, target_stride,

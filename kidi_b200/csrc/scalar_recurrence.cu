@@ -58,113 +58,248 @@ struct ShortConvArgs {
 namespace {
 
 constexpr int THREADS = 256;
-constexpr int COLUMNS = 32;
-constexpr int GROUPS = THREADS / COLUMNS;
 constexpr int MAX_CHUNK = 16;
 constexpr int MAX_TAPS = 32;
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + expf(-x)); }
 
-// R: state rows a thread keeps in registers (dim <= GROUPS * R).
-template <typename T, int R>
-__global__ void __launch_bounds__(THREADS) scalar_recurrence_kernel(ScalarRecurrenceArgs a) {
+// A load that stays where it is written and hands back the bits as they are, so that a chunk's loads are issued
+// together, wait in registers while the chunk before is walked, and are converted only where they are used.
+template <typename T> struct Raw;
+template <> struct Raw<float> {
+    typedef float type;
+    static __device__ __forceinline__ type load(const float* pointer) {
+        float value;
+        asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(value) : "l"(pointer));
+        return value;
+    }
+    static __device__ __forceinline__ float value(type bits) { return bits; }
+};
+template <> struct Raw<bf16> {
+    typedef unsigned short type;
+    static __device__ __forceinline__ type load(const bf16* pointer) {
+        unsigned short bits;
+        asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(bits) : "l"(pointer));
+        return bits;
+    }
+    static __device__ __forceinline__ float value(type bits) { return __uint_as_float((unsigned)bits << 16); }
+};
+
+// R: state rows a thread keeps in registers (dim <= GROUPS * R). Eight warps walk the block's 32 columns; warp g
+// owns the state rows g R .. g R + R - 1. A ninth warp keeps, in the block of the head's first columns, the extra
+// column (the state's rows dealt out over its lanes): its value is 1 for every token, so it needs no column of a
+// block of its own. The keys (times b_t), queries (times q_scale), values and decays of a chunk of tokens are
+// staged in shared memory a chunk ahead: their loads are issued before the chunk before is walked. COLUMNS: the
+// state columns of a block, one a lane of a group of COLUMNS lanes (32: a warp; 16: half a warp, for steps that
+// would otherwise leave most SMs without a block); GROUPS = 256 / COLUMNS groups share the state's rows.
+template <typename T, int R, int COLUMNS>
+__global__ void __launch_bounds__(THREADS + 32) scalar_recurrence_kernel(ScalarRecurrenceArgs a) {
+    extern __shared__ __align__(16) float shared[];
+    constexpr int GROUPS = THREADS / COLUMNS;
     constexpr int PADDED = GROUPS * R;
-    constexpr int CHUNK = R >= 32 ? MAX_CHUNK / 2 : MAX_CHUNK;     // tokens staged at a time (48 KB of shared memory)
-    __shared__ float keys[CHUNK][PADDED];        // b_t k_t
-    __shared__ float queries[CHUNK][PADDED];     // q_t * q_scale
-    __shared__ float values[CHUNK][COLUMNS];
-    __shared__ float decay[CHUNK];
-    __shared__ float partial[CHUNK][GROUPS][COLUMNS];
+    constexpr int CHUNK = R >= 32 ? MAX_CHUNK / 2 : MAX_CHUNK;     // tokens staged at a time
+    constexpr int ROW = 2 * PADDED + COLUMNS + 4;                  // keys | queries | values | decay (and padding)
+    constexpr int KQ = (CHUNK * PADDED + THREADS - 1) / THREADS;
+    constexpr int VV = (CHUNK * COLUMNS + THREADS - 1) / THREADS;
+    constexpr int NR = (PADDED + 31) / 32;                         // rows of the extra column a lane keeps
+    float* stage = shared;                                         // [2][CHUNK][ROW]
+    float* partials = shared + 2 * CHUNK * ROW;                    // [2][CHUNK][GROUPS][COLUMNS]
+    float* counted = partials + 2 * CHUNK * THREADS;               // [2][CHUNK][32]: the extra column's parts, a lane each
     const int seq = blockIdx.x, head = blockIdx.y;
     const int row0 = a.seq_row0[seq], count = a.seq_len[seq];
     if (count <= 0 || a.row_seq[row0] < 0) return;        // a padding sequence touches no state
     const int dim = a.dim, vdim = a.vdim, vcols = a.vdim + a.extra;
-    const int lane = threadIdx.x % COLUMNS, g = threadIdx.x / COLUMNS;
+    const bool walker = threadIdx.x < THREADS;
+    const bool counter = !walker && a.extra && blockIdx.z == 0;    // the warp that keeps the extra column
+    const int lane = walker ? threadIdx.x % COLUMNS : threadIdx.x & 31, g = (threadIdx.x / COLUMNS) % GROUPS;
     const int column = blockIdx.z * COLUMNS + lane;
-    const bool live = column < vcols;
+    const bool live = walker && column < vdim;
     const int k_head = head / (a.heads / a.k_heads), q_head = head / (a.heads / a.q_heads);
     float* state = a.state + ((long long)a.seq_slot[seq] * a.heads + head) * dim * vcols;
-    float S[R];
+    float S[R], N[NR];
 #pragma unroll
     for (int j = 0; j < R; ++j) {
         const int d = g * R + j;
         S[j] = live && d < dim ? state[(long long)d * vcols + column] : 0.f;
     }
-    for (int t0 = 0; t0 < count; t0 += CHUNK) {
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int d = lane + 32 * j;
+        N[j] = counter && d < dim ? state[(long long)d * vcols + vdim] : 0.f;
+    }
+    typename Raw<T>::type raw_k[KQ], raw_q[KQ], raw_v[VV];
+    float raw_write[KQ], raw_keep = 1.f;
+
+    auto fetch = [&](int t0) {
+        if (!walker) return;
         const int tokens = min(CHUNK, count - t0);
-        for (int index = threadIdx.x; index < tokens * PADDED; index += THREADS) {
-            const int t = index / PADDED, d = index - t * PADDED;
-            const long long row = row0 + t0 + t;
-            float key = 0.f, query = 0.f;
-            if (d < dim) {
-                const float write = a.coef[(row * a.heads + head) * a.coef_width + 1];
-                key = write * to_float(((const T*)a.k)[row * a.ldk + (long long)k_head * dim + d]);
-                query = a.q_scale * to_float(((const T*)a.q)[row * a.ldq + (long long)q_head * dim + d]);
+#pragma unroll
+        for (int i = 0; i < KQ; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
+            raw_k[i] = raw_q[i] = 0;
+            raw_write[i] = 0.f;
+            if (t < tokens && d < dim) {
+                const long long row = row0 + t0 + t;
+                raw_k[i] = Raw<T>::load((const T*)a.k + row * a.ldk + (long long)k_head * dim + d);
+                raw_q[i] = Raw<T>::load((const T*)a.q + row * a.ldq + (long long)q_head * dim + d);
+                raw_write[i] = Raw<float>::load(a.coef + (row * a.heads + head) * a.coef_width + 1);
             }
-            keys[t][d] = key;
-            queries[t][d] = query;
         }
-        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS) {
-            const int t = index / COLUMNS, c = index - t * COLUMNS;
+#pragma unroll
+        for (int i = 0; i < VV; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
             const int col = blockIdx.z * COLUMNS + c;
-            const long long row = row0 + t0 + t;
-            float value = 0.f;
-            if (col < vdim) value = to_float(((const T*)a.v)[row * a.ldv + (long long)head * vdim + col]);
-            else if (col < vcols) value = 1.f;
-            values[t][c] = value;
+            raw_v[i] = 0;
+            if (t < tokens && col < vdim)
+                raw_v[i] = Raw<T>::load((const T*)a.v + (long long)(row0 + t0 + t) * a.ldv + (long long)head * vdim + col);
         }
         if (threadIdx.x < tokens)
-            decay[threadIdx.x] = a.coef[((long long)(row0 + t0 + threadIdx.x) * a.heads + head) * a.coef_width];
-        __syncthreads();
-        for (int t = 0; t < tokens; ++t) {
-            const float keep = decay[t], value = values[t][lane];
-            const float* key = &keys[t][g * R];            // one address a group of lanes: broadcasts
-            const float* query = &queries[t][g * R];
-            float sum = 0.f;
+            raw_keep = Raw<float>::load(a.coef + ((long long)(row0 + t0 + threadIdx.x) * a.heads + head) * a.coef_width);
+    };
+    auto put = [&](float* target) {
+        if (!walker) return;
 #pragma unroll
-            for (int j = 0; j < R; ++j) {
-                const float s = fmaf(keep, S[j], key[j] * value);
-                S[j] = s;
-                sum = fmaf(s, query[j], sum);
-            }
-            partial[t][g][lane] = sum;
+        for (int i = 0; i < KQ; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / PADDED, d = index - t * PADDED;
+            if (index >= CHUNK * PADDED) continue;
+            target[t * ROW + d] = raw_write[i] * Raw<T>::value(raw_k[i]);
+            target[t * ROW + PADDED + d] = a.q_scale * Raw<T>::value(raw_q[i]);
         }
+#pragma unroll
+        for (int i = 0; i < VV; ++i) {
+            const int index = threadIdx.x + i * THREADS, t = index / COLUMNS, c = index - t * COLUMNS;
+            if (index < CHUNK * COLUMNS) target[t * ROW + 2 * PADDED + c] = Raw<T>::value(raw_v[i]);
+        }
+        if (threadIdx.x < CHUNK) target[threadIdx.x * ROW + 2 * PADDED + COLUMNS] = raw_keep;
+    };
+
+    fetch(0);
+    put(stage);
+    __syncthreads();
+    int turn = 0;
+    for (int t0 = 0; t0 < count; t0 += CHUNK, turn ^= 1) {
+        const int tokens = min(CHUNK, count - t0);
+        const bool more = t0 + CHUNK < count;
+        if (more) fetch(t0 + CHUNK);                     // on their way while this chunk is walked
+        const float* __restrict__ current = stage + turn * (CHUNK * ROW);
+        float* __restrict__ partial = partials + turn * (CHUNK * GROUPS * COLUMNS);
+        if (walker) {
+#pragma unroll 2
+            for (int t = 0; t < tokens; ++t) {       // (two tokens an iteration: the second one's loads go out early)
+                const float* key = current + t * ROW + g * R;        // one address a warp: broadcasts
+                const float* query = key + PADDED;
+                const float keep = current[t * ROW + 2 * PADDED + COLUMNS];
+                const float value = current[t * ROW + 2 * PADDED + lane];
+                float sum = 0.f;
+                if constexpr (R % 4 == 0) {
+                    float sums[4] = {0.f, 0.f, 0.f, 0.f};            // four chains instead of one of R links
+#pragma unroll
+                    for (int j = 0; j < R; j += 4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(key + j);
+                        const float4 q4 = *reinterpret_cast<const float4*>(query + j);
+                        const float kj[4] = {k4.x, k4.y, k4.z, k4.w}, qj[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float s = fmaf(keep, S[j + e], kj[e] * value);
+                            S[j + e] = s;
+                            sums[e] = fmaf(s, qj[e], sums[e]);
+                        }
+                    }
+                    sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < R; ++j) {
+                        const float s = fmaf(keep, S[j], key[j] * value);
+                        S[j] = s;
+                        sum = fmaf(s, query[j], sum);
+                    }
+                }
+                partial[(t * GROUPS + g) * COLUMNS + lane] = sum;
+            }
+        } else if (counter) {
+            for (int t = 0; t < tokens; ++t) {
+                const float* key = current + t * ROW;
+                const float keep = current[t * ROW + 2 * PADDED + COLUMNS];
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < NR; ++j) {
+                    const int d = lane + 32 * j;
+                    if (d < PADDED) {
+                        N[j] = fmaf(keep, N[j], key[d]);
+                        sum = fmaf(N[j], key[PADDED + d], sum);
+                    }
+                }
+                counted[(turn * CHUNK + t) * 32 + lane] = sum;      // added up behind the barrier: no chain of
+            }                                                        // shuffles a token holds the walkers up
+        }
+        if (more) put(stage + (turn ^ 1) * (CHUNK * ROW));
         __syncthreads();
-        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS) {
+        // (the stage and the partials written next are the other ones; these are free again behind the next barrier)
+        for (int index = threadIdx.x; index < tokens * COLUMNS; index += THREADS + 32) {
             const int t = index / COLUMNS, c = index - t * COLUMNS;
             const int col = blockIdx.z * COLUMNS + c;
-            if (col >= vcols) continue;
+            if (col >= vdim) continue;
             float total = 0.f;
 #pragma unroll
-            for (int k = 0; k < GROUPS; ++k) total += partial[t][k][c];
+            for (int k = 0; k < GROUPS; ++k) total += partial[(t * GROUPS + k) * COLUMNS + c];
             a.out[((long long)(row0 + t0 + t) * a.heads + head) * vcols + col] = total;
         }
-        // (the next chunk's staging writes keys, queries, values and decay, which nobody reads any more; its walk
-        // writes `partial` only behind the next barrier)
+        if (a.extra && blockIdx.z == 0 && threadIdx.x < tokens) {      // n . q of the chunk's tokens, a thread each
+            float total = 0.f;
+#pragma unroll
+            for (int l = 0; l < 32; ++l) total += counted[(turn * CHUNK + threadIdx.x) * 32 + l];
+            a.out[((long long)(row0 + t0 + threadIdx.x) * a.heads + head) * vcols + vdim] = total;
+        }
     }
 #pragma unroll
     for (int j = 0; j < R; ++j) {
         const int d = g * R + j;
         if (live && d < dim) state[(long long)d * vcols + column] = S[j];
     }
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int d = lane + 32 * j;
+        if (counter && d < dim) state[(long long)d * vcols + vdim] = N[j];
+    }
 }
 
-template <typename T, int R>
+template <typename T, int R, int COLUMNS>
 int launch_recurrence(const ScalarRecurrenceArgs& a, cudaStream_t stream) {
-    dim3 grid(a.seqs, a.heads, (a.vdim + a.extra + COLUMNS - 1) / COLUMNS);
-    return kidi_launch(scalar_recurrence_kernel<T, R>, grid, THREADS, 0, stream, a);
+    constexpr int GROUPS = THREADS / COLUMNS;
+    constexpr int PADDED = GROUPS * R;
+    constexpr int CHUNK = R >= 32 ? MAX_CHUNK / 2 : MAX_CHUNK;
+    const size_t shared = (size_t)2 * CHUNK * ((2 * PADDED + COLUMNS + 4) + GROUPS * COLUMNS + 32) * sizeof(float);
+    auto kernel = scalar_recurrence_kernel<T, R, COLUMNS>;
+    if (shared > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (status != cudaSuccess) return (int)status;
+    }
+    dim3 grid(a.seqs, a.heads, (a.vdim + COLUMNS - 1) / COLUMNS);
+    return kidi_launch(kernel, grid, THREADS + 32, shared, stream, a);
+}
+
+template <typename T, int COLUMNS>
+int dispatch_rows(const ScalarRecurrenceArgs& a, cudaStream_t stream) {
+    constexpr int GROUPS = THREADS / COLUMNS;
+    const int rows = (a.dim + GROUPS - 1) / GROUPS;
+    if (rows <= 1) return launch_recurrence<T, 1, COLUMNS>(a, stream);
+    if (rows <= 2) return launch_recurrence<T, 2, COLUMNS>(a, stream);
+    if (rows <= 4) return launch_recurrence<T, 4, COLUMNS>(a, stream);
+    if (rows <= 8) return launch_recurrence<T, 8, COLUMNS>(a, stream);
+    if (rows <= 16) return launch_recurrence<T, 16, COLUMNS>(a, stream);
+    if (COLUMNS == 32 && rows <= 32) return launch_recurrence<T, 32, 32>(a, stream);
+    return KIDI_REFUSED_SIZE;
 }
 
 template <typename T>
 int dispatch_recurrence(const ScalarRecurrenceArgs& a, cudaStream_t stream) {
-    const int rows = (a.dim + GROUPS - 1) / GROUPS;
-    if (rows <= 1) return launch_recurrence<T, 1>(a, stream);
-    if (rows <= 2) return launch_recurrence<T, 2>(a, stream);
-    if (rows <= 4) return launch_recurrence<T, 4>(a, stream);
-    if (rows <= 8) return launch_recurrence<T, 8>(a, stream);
-    if (rows <= 16) return launch_recurrence<T, 16>(a, stream);
-    if (rows <= 32) return launch_recurrence<T, 32>(a, stream);
-    return KIDI_REFUSED_SIZE;
+    // Few (sequence, head, 32 columns) blocks: half as many columns a block, so that SMs hold two blocks or more (a
+    // block's walk is a chain of dependent steps: an SM needs several to fill its issue slots). The choice
+    // depends on the step's sizes only through the number of sequences; a row's result does not depend on it
+    // beyond the order in which the partial read-outs are added.
+    const long long blocks = (long long)a.seqs * a.heads * ((a.vdim + 31) / 32);
+    if (blocks < 2 * 148 && a.vdim > 16) return dispatch_rows<T, 16>(a, stream);
+    return dispatch_rows<T, 32>(a, stream);
 }
 
 // ---------------------------------------------------------------- short causal convolution with carried inputs
@@ -335,7 +470,7 @@ KIDI_API int kidi_scalar_recurrence(const ScalarRecurrenceArgs* args, int dtype,
     if (a.seqs <= 0) return 0;
     if (a.heads <= 0 || a.heads > 65535 || a.dim <= 0 || a.vdim <= 0 || a.extra < 0 || a.extra > 1 || a.k_heads <= 0 ||
         a.q_heads <= 0 || a.heads % a.k_heads || a.heads % a.q_heads || a.coef_width < 2 ||
-        (a.vdim + a.extra + COLUMNS - 1) / COLUMNS > 65535)
+        (a.vdim + 15) / 16 > 65535)
         return KIDI_REFUSED_SIZE;
     if (dtype == KIDI_F32) return dispatch_recurrence<float>(a, stream);
     if (dtype == KIDI_BF16) return dispatch_recurrence<bf16>(a, stream);
