@@ -160,6 +160,61 @@ __global__ void lanes_mix_x4_kernel(const float* source, long long source_stride
     }
 }
 
+// lanes_mix and lanes_rmsnorm in one pass (widths that are multiples of four): a block per output row forms the new
+// lanes from the old ones and the sublayer's result y, writes them (unless only picked rows are wanted: the stream is
+// then left as it is), and reads them at once as the next sublayer's weighted sum, with its norm. Every sum is formed in
+// the order of the two kernels it replaces: the same bits.
+template <typename TD, typename TW, typename TY>
+__global__ void __launch_bounds__(LANE_THREADS)
+lanes_mix_rmsnorm_kernel(const float* source, long long source_stride, float* target, long long target_stride, int count,
+                         const float* __restrict__ mix, const float* __restrict__ write, const TD* __restrict__ delta,
+                         const float* __restrict__ read, const TW* __restrict__ weight, TY* __restrict__ y,
+                         const int* __restrict__ row_index, int hidden, float eps) {
+    extern __shared__ __align__(16) float staged[];
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const long long s = row_index ? row_index[r] : r;
+    float square = 0.f;
+    for (int c = 4 * threadIdx.x; c < hidden; c += 4 * LANE_THREADS) {
+        float old[MAX_LANES][4], d[4], sum[4];
+#pragma unroll
+        for (int l = 0; l < MAX_LANES; ++l)
+            if (l < count) load4(source + l * source_stride + s * hidden + c, old[l]);
+        load4(delta + s * hidden + c, d);
+#pragma unroll
+        for (int t = 0; t < MAX_LANES; ++t) {
+            if (t >= count) break;
+            float fresh[4];
+#pragma unroll
+            for (int l = 0; l < MAX_LANES; ++l)
+                if (l < count) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        fresh[i] = l == 0 ? mix[t] * old[0][i] : fmaf(mix[l * count + t], old[l][i], fresh[i]);
+                }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                fresh[i] = fmaf(write[t], d[i], fresh[i]);
+                sum[i] = t == 0 ? (read ? read[0] * fresh[i] : fresh[i])
+                                : (read ? fmaf(read[t], fresh[i], sum[i]) : sum[i] + fresh[i]);
+            }
+            if (!row_index) store4(target + t * target_stride + s * hidden + c, fresh);
+        }
+        store4(staged + c, sum);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) square = fmaf(sum[i], sum[i], square);
+    }
+    const float inv = 1.0f / sqrtf(block_sum<LANE_THREADS>(square, scratch) / (float)hidden + eps);
+    for (int c = 4 * threadIdx.x; c < hidden; c += 4 * LANE_THREADS) {
+        float value[4], w[4];
+        load4(staged + c, value);
+        load4(weight + c, w);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) value[i] = value[i] * inv * w[i];
+        store4(y + (long long)r * hidden + c, value);
+    }
+}
+
 // One block per row: both rows staged, their mean squares, then the weighted sum of the two normalised rows.
 template <typename T, typename TY>
 __global__ void __launch_bounds__(LANE_THREADS)
@@ -299,6 +354,63 @@ KIDI_API int kidi_lanes_mix(const float* source, long long source_stride, float*
     if (y_dtype == KIDI_BF16)
         return kidi_launch(lanes_mix_kernel<bf16>, blocks, 256, 0, stream, source, source_stride, target, target_stride,
                            count, mix, write, (const bf16*)y, total);
+    return KIDI_REFUSED_DTYPE;
+}
+
+namespace {
+template <typename TD, typename TW>
+int lanes_mix_rmsnorm_out(const float* source, long long source_stride, float* target, long long target_stride, int count,
+                          const float* mix, const float* write, const TD* delta, const float* read, const TW* weight,
+                          void* y, int y_dtype, const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
+    const size_t shared = (size_t)hidden * sizeof(float);
+    if (y_dtype == KIDI_F32) {
+        auto kernel = lanes_mix_rmsnorm_kernel<TD, TW, float>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, source, source_stride, target, target_stride, count,
+                           mix, write, delta, read, weight, (float*)y, row_index, hidden, eps);
+    }
+    if (y_dtype == KIDI_BF16) {
+        auto kernel = lanes_mix_rmsnorm_kernel<TD, TW, bf16>;
+        if (shared > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        return kidi_launch(kernel, rows, LANE_THREADS, shared, stream, source, source_stride, target, target_stride, count,
+                           mix, write, delta, read, weight, (bf16*)y, row_index, hidden, eps);
+    }
+    return KIDI_REFUSED_DTYPE;
+}
+
+template <typename TD>
+int lanes_mix_rmsnorm_weight(const float* source, long long source_stride, float* target, long long target_stride,
+                             int count, const float* mix, const float* write, const TD* delta, const float* read,
+                             const void* weight, int weight_dtype, void* y, int y_dtype, const int* row_index, int rows,
+                             int hidden, float eps, cudaStream_t stream) {
+    if (weight_dtype == KIDI_F32)
+        return lanes_mix_rmsnorm_out<TD, float>(source, source_stride, target, target_stride, count, mix, write, delta,
+                                                read, (const float*)weight, y, y_dtype, row_index, rows, hidden, eps, stream);
+    if (weight_dtype == KIDI_BF16)
+        return lanes_mix_rmsnorm_out<TD, bf16>(source, source_stride, target, target_stride, count, mix, write, delta, read,
+                                               (const bf16*)weight, y, y_dtype, row_index, rows, hidden, eps, stream);
+    return KIDI_REFUSED_DTYPE;
+}
+}  // namespace
+
+// Refuses (KIDI_REFUSED_SIZE) what the four-element form does not take; the caller then runs the two kernels.
+KIDI_API int kidi_lanes_mix_rmsnorm(const float* source, long long source_stride, float* target, long long target_stride,
+                                    int count, const float* mix, const float* write, const void* delta, int delta_dtype,
+                                    const float* read, const void* weight, int weight_dtype, void* y, int y_dtype,
+                                    const int* row_index, int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (count <= 0 || count > MAX_LANES || hidden <= 0 || hidden % 4 || (size_t)hidden * sizeof(float) > 200 * 1024 ||
+        source_stride % 4 || target_stride % 4 || !weight || ((uintptr_t)source & 15) || ((uintptr_t)target & 15) ||
+        ((uintptr_t)delta & 15) || ((uintptr_t)weight & 15) || ((uintptr_t)y & 15))
+        return KIDI_REFUSED_SIZE;
+    if (delta_dtype == KIDI_F32)
+        return lanes_mix_rmsnorm_weight<float>(source, source_stride, target, target_stride, count, mix, write,
+                                               (const float*)delta, read, weight, weight_dtype, y, y_dtype, row_index, rows,
+                                               hidden, eps, stream);
+    if (delta_dtype == KIDI_BF16)
+        return lanes_mix_rmsnorm_weight<bf16>(source, source_stride, target, target_stride, count, mix, write,
+                                              (const bf16*)delta, read, weight, weight_dtype, y, y_dtype, row_index, rows,
+                                              hidden, eps, stream);
     return KIDI_REFUSED_DTYPE;
 }
 

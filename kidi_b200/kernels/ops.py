@@ -188,6 +188,10 @@ def core():
                                            c_void_p, c_int, c_int, c_float, c_void_p]
         lib.kidi_lanes_mix.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p,
                                        c_int, c_longlong, c_void_p]
+        lib.kidi_lanes_mix_rmsnorm.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p,
+                                               c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                               c_int, c_int, c_float, c_void_p]
+        lib.kidi_lanes_mix_rmsnorm.restype = c_int
         lib.kidi_normed_pair_sum.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
                                              c_int, c_int, c_int, c_float, c_void_p]
         lib.kidi_sigmoid_gate.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p]
@@ -550,6 +554,43 @@ def lanes_mix(source: torch.Tensor, target: torch.Tensor, mix: torch.Tensor, wri
     _check(core().kidi_lanes_mix(_ptr(source), source.stride(0), _ptr(target), target.stride(0), count, _ptr(mix),
                                  _ptr(write), _ptr(y), dtype_code(y.dtype), y.numel(), _stream()), "lanes_mix")
     return target
+
+
+def lanes_mix_rmsnorm(source: torch.Tensor, target: torch.Tensor, mix: torch.Tensor, write: torch.Tensor,
+                      y: torch.Tensor, read: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                      out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`lanes_mix` and then `lanes_rmsnorm` of the new lanes, in one kernel where the width allows (else in two): the
+    lanes are updated (target[t] = sum_s mix[s, t] source[s] + write[t] y) and read at once as sum_t read[t]
+    target[t], normalised. With `row_index` only those rows are produced and no lane is written (the update is then
+    lost: for the last reader of a stream)."""
+    _need_cuda(source, target, mix, write, y, read, weight, row_index)
+    count, rows_in, hidden = target.shape
+    rows = row_index.shape[0] if row_index is not None else rows_in
+    fits = (hidden % 4 == 0 and weight is not None and source.dim() == 3 and source.shape == target.shape
+            and all(lanes.dtype == torch.float32 and lanes.stride(2) == 1 and lanes.stride(1) == hidden
+                    for lanes in (source, target)) and y.shape == (rows_in, hidden) and y.is_contiguous())
+    if fits:
+        _float_vector(read, count, "the lanes' read weights")
+        _float_vector(write, count, "the lanes' write weights")
+        if mix.dtype != torch.float32 or mix.shape != (count, count) or not mix.is_contiguous():
+            raise invalid_argument("lanes_mix: the mixing matrix is float32 [count, count]")
+        if weight.shape != (hidden,) or not weight.is_contiguous():
+            raise invalid_argument(f"the norm weight must have {hidden} elements")
+        out = torch.empty((rows, hidden), dtype=out_dtype, device=target.device)
+        status = core().kidi_lanes_mix_rmsnorm(
+            _ptr(source), source.stride(0), _ptr(target), target.stride(0), count, _ptr(mix), _ptr(write), _ptr(y),
+            dtype_code(y.dtype), _ptr(read), _ptr(weight), dtype_code(weight.dtype), _ptr(out), dtype_code(out_dtype),
+            _ptr(row_index), rows, hidden, float(eps), _stream())
+        if status != -3:
+            _check(status, "lanes_mix_rmsnorm")
+            return out
+    if row_index is not None:      # the stream stays as it is: the new lanes of the picked rows go to scratch memory
+        picked = row_index.long()
+        source, y = source[:, picked].contiguous(), y[picked].contiguous()
+        target = torch.empty_like(source)
+        row_index = None
+    lanes_mix(source, target, mix, write, y)
+    return lanes_rmsnorm(target, read, weight, eps, out_dtype, row_index=row_index)
 
 
 def normed_pair_sum(a: torch.Tensor, b: torch.Tensor, weight_a: torch.Tensor, weight_b: torch.Tensor, eps: float,

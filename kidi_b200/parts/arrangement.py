@@ -184,8 +184,8 @@ class HyperConnectionBlock(Part):
 
         u = sum_s in_q[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix_q[s, t] x_s + out_q[t] y    (all t at once)
 
-    The sum that a norm reads is formed in the norm's kernel, the update of all lanes in one kernel; lanes, sums
-    and updates are 32-bit. After the last block the stream is the sum of the lanes (the norm before the head reads
+    The sum that a norm reads is formed in the norm's kernel, and so is the update of the lanes before it (it waits
+    in `ResidualStream.lane_update` for the next norm, as a residual delta does); lanes, sums and updates are 32-bit. After the last block the stream is the sum of the lanes (the norm before the head reads
     that sum). Parameters: hidden_size, streams, and the tensor names under the prefix: in1, out1, mix1, in2, out2,
     mix2 (defaults hc1.in, hc1.out, hc1.mix, hc2.in, hc2.out, hc2.mix)."""
 
@@ -236,12 +236,9 @@ class HyperConnectionBlock(Part):
         return self.input_norm
 
     def _write(self, stream: ResidualStream, number: str, result: torch.Tensor) -> None:
-        from ..kernels import ops
-        source = stream.lanes
-        if source.stride(0) == 0:        # still one matrix that stands for every lane: the lanes get memory now
-            stream.lanes = torch.empty(source.shape, dtype=torch.float32, device=source.device)
-        ops.lanes_mix(source, stream.lanes, self.weights["mix" + number], self.weights["out" + number],
-                      result.contiguous())
+        """The update waits for the norm that reads the lanes next, which applies it in its own kernel."""
+        stream.apply_lane_update()
+        stream.lane_update = (self.weights["mix" + number], self.weights["out" + number], result.contiguous())
 
     def forward(self, stream: ResidualStream, ctx, views, owns_cache: bool) -> None:
         if stream.lanes is None:

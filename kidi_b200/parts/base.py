@@ -167,6 +167,9 @@ class ResidualStream:
         # arrangement): once set, the lanes are the stream, `hidden` is no longer kept up to date, and a norm reads a
         # weighted sum of the lanes (their plain sum, for the norm before the head).
         self.lanes: Optional[torch.Tensor] = None
+        # An update of the lanes that the next norm applies in its own kernel, as it applies a pending delta:
+        # (mix [lanes, lanes], write [lanes], y [rows, hidden]): lane'_t = sum_s mix[s, t] lane_s + write[t] y.
+        self.lane_update: Optional[tuple] = None
 
     def add(self, delta: Optional[torch.Tensor], normed_by=None) -> None:
         """`delta` None: the part that made it has added it through a sink already. `normed_by`: a norm part
@@ -179,6 +182,22 @@ class ResidualStream:
         self.pending = delta
         self.pending_norm = normed_by
         self.prepared = None          # rows prepared before this delta are no longer the stream's
+
+    def lane_target(self) -> torch.Tensor:
+        """The lanes as memory that an update may write: while one matrix still stands for every lane (a view with a
+        lane stride of 0), the lanes get memory of their own here and the view stays what the update reads."""
+        if self.lanes.stride(0) == 0:
+            return torch.empty(self.lanes.shape, dtype=torch.float32, device=self.lanes.device)
+        return self.lanes
+
+    def apply_lane_update(self) -> None:
+        """Applies a waiting update of the lanes in a kernel of its own (for a reader that cannot do it itself)."""
+        if self.lane_update is not None:
+            from ..kernels import ops
+            mix, write, y = self.lane_update
+            target = self.lane_target()
+            ops.lanes_mix(self.lanes, target, mix, write, y)
+            self.lanes, self.lane_update = target, None
 
     def take_pending(self) -> Optional[torch.Tensor]:
         """The delta that the caller must add. A delta that still has to pass a norm of its own is normalised

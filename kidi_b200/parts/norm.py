@@ -59,6 +59,14 @@ class RMSNorm(Part):
         if stream.lanes is not None:
             if self.offset and self.weight.dtype != torch.float32:
                 raise RuntimeError("a norm with a weight offset keeps its weight in 32-bit")
+            if stream.lane_update is not None:        # the lanes' waiting update and this read in one kernel
+                mix, write, y = stream.lane_update
+                target = stream.lane_target()
+                normed = ops.lanes_mix_rmsnorm(stream.lanes, target, mix, write, y, read, self.weight, self.eps,
+                                               out_dtype or self.env.dtype, row_index=rows)
+                if rows is None:
+                    stream.lanes, stream.lane_update = target, None
+                return normed
             return ops.lanes_rmsnorm(stream.lanes, read, self.weight, self.eps, out_dtype or self.env.dtype,
                                      row_index=rows)
         prepared = stream.take_prepared(self) if rows is None else None

@@ -98,7 +98,7 @@ def test_the_lanes_kernels(dtype):
     from kidi_b200.kernels import ops
     generator = torch.Generator().manual_seed(3)
     loose = 1e-5 if dtype == torch.float32 else 3e-2
-    for count, rows, hidden in ((1, 5, 40), (2, 9, 72), (3, 4, 256), (8, 3, 24)):
+    for count, rows, hidden in ((1, 5, 40), (2, 9, 72), (3, 4, 256), (8, 3, 24), (2, 7, 30)):
         lanes = torch.randn(count, rows, hidden, generator=generator).cuda()
         read = torch.randn(count, generator=generator).cuda()
         weight = (torch.randn(hidden, generator=generator) * 0.3 + 1).to(dtype).cuda()
@@ -124,6 +124,16 @@ def test_the_lanes_kernels(dtype):
         new = mix.double().cpu().sum(0)[:, None, None] * one.double().cpu()[None] \
             + write.double().cpu()[:, None, None] * y.double().cpu()[None]
         assert torch.allclose(target.double().cpu(), new, atol=1e-5)
+        # update and read in one kernel: the same bits as the two kernels, also at picked rows (which leave the lanes)
+        before = torch.randn(count, rows, hidden, generator=generator).cuda()
+        apart = torch.empty_like(before)
+        ops.lanes_mix(before, apart, mix, write, y)
+        fused = before.clone()
+        got = ops.lanes_mix_rmsnorm(fused, fused, mix, write, y, read, weight, 1e-5, dtype)
+        assert torch.equal(fused, apart) and torch.equal(got, ops.lanes_rmsnorm(apart, read, weight, 1e-5, dtype))
+        kept = before.clone()
+        got = ops.lanes_mix_rmsnorm(kept, kept, mix, write, y, None, weight, 1e-5, dtype, row_index=index)
+        assert torch.equal(kept, before) and torch.equal(got, ops.lanes_rmsnorm(apart, None, weight, 1e-5, dtype, row_index=index))
         a, b = (torch.randn(rows, hidden, generator=generator).mul(3).to(dtype).cuda() for _ in range(2))
         wa, wb = (torch.randn(hidden, generator=generator).mul(0.3).add(1).cuda() for _ in range(2))
         want = 0.5 * plain_biropel.rms_norm(a.double().cpu(), wa.double().cpu(), 1e-4) \
@@ -440,7 +450,7 @@ def test_which_kernels_run(record_property):
         run(engine, slot, tokens[:299], want=[])
     record_property("prompt kernels", sorted(set(names)))
     assert sum(name.startswith("attention_prefill") for name in names) >= 3
-    assert names.count("scalar_recurrence") == 2 and names.count("lanes_mix") == 9 and "short_conv_state" in names
+    assert names.count("scalar_recurrence") == 2 and names.count("lanes_mix_rmsnorm") == 8 and "short_conv_state" in names
     with ops.record_launches() as names:
         last = run(engine, slot, tokens[299:])
     record_property("decode kernels", sorted(set(names)))
