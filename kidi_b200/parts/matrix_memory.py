@@ -10,7 +10,9 @@ With h the mixer's input, H heads, d the width of a query or key head and e the 
 
 Each head's o is divided by its root mean square; the heads are concatenated, multiplied by a weight [H e] and by
 sigmoid(W_g h), and projected by W_o. What a sequence keeps, as fixed-size 32-bit state per cache slot: S with n as
-one more column, [H, d, e + 1], and m [H]. Gates, the maximum, the state, the read-out and the norm are 32-bit.
+one more column, [H, d, e + 1], and m [H]. Gates, the maximum, the state, the read-out and the norm are 32-bit; so are
+the results of the two gate projections (a product of their own, 2 H rows): a log gate of up to `gate_cap` rounded to
+bfloat16 would be off by up to a sixteenth, which the exponential turns into six per cent of a write strength.
 
 Parameters (`spec.params`): hidden_size, num_heads, dim, vdim, gate_cap, eps, and the tensor names under the prefix:
 q, k, v, g, o, norm, i, i_bias, f, f_bias.
@@ -49,18 +51,20 @@ class MatrixMemory(Part):
         if self.dim > kernels.MAX_DIM:
             raise unsupported(f"a memory of {self.dim} rows a head exceeds {kernels.MAX_DIM}, the most the kernel takes")
         self.qk_width, self.v_width = self.heads * self.dim, self.heads * self.vdim
-        self.width = 2 * self.qk_width + 2 * self.v_width + 2 * self.heads      # [q | k | v | g | i | f]
+        self.width = 2 * self.qk_width + 2 * self.v_width                       # [q | k | v | g]; [i | f] apart
         self.names = {key: spec.param(key + "_name", default) for key, default in NAMES.items()}
         self.projection: Optional[Linear] = None
+        self.gate_projection: Optional[Linear] = None
         self.out: Optional[Linear] = None
         self.norm = None
 
     def parameter_specs(self) -> List[ParamSpec]:
         n, hidden = self.names, self.hidden
         return [
-            ParamSpec("qkvgif", (self.width, hidden), sources=(
+            ParamSpec("qkvg", (self.width, hidden), sources=(
                 (n["q"], (self.qk_width, hidden)), (n["k"], (self.qk_width, hidden)), (n["v"], (self.v_width, hidden)),
-                (n["g"], (self.v_width, hidden)), (n["i"], (self.heads, hidden)), (n["f"], (self.heads, hidden)))),
+                (n["g"], (self.v_width, hidden)))),
+            ParamSpec("if", (2 * self.heads, hidden), sources=((n["i"], (self.heads, hidden)), (n["f"], (self.heads, hidden)))),
             ParamSpec("if.bias", (2 * self.heads,), init=("normal", 1.0), sources=(
                 (n["i_bias"], (self.heads,)), (n["f_bias"], (self.heads,)))),
             ParamSpec(n["norm"], (self.v_width,), init=("one_plus_normal", 0.1)),
@@ -69,14 +73,18 @@ class MatrixMemory(Part):
 
     def bind(self, tensors) -> None:
         n = self.names
-        fused = tensors["qkvgif"]
-        rows = fused.shape[0] + (-fused.shape[0] % 8)      # rows of the product's result start on 16-byte boundaries
-        if rows != fused.shape[0]:
-            pad = torch.zeros((rows - fused.shape[0], self.hidden), dtype=fused.dtype, device=fused.device)
-            fused = torch.cat([fused, pad], dim=0).contiguous()
-        bias = torch.zeros(rows, dtype=torch.float32, device=fused.device)
-        bias[self.width - 2 * self.heads:self.width] = tensors["if.bias"].float()
-        self.projection, self.out = Linear(fused, bias), Linear(tensors[n["o"]])
+        def padded(matrix):        # rows of a product's result start on 16-byte boundaries
+            extra = -matrix.shape[0] % 8
+            if not extra:
+                return matrix
+            pad = torch.zeros((extra, self.hidden), dtype=matrix.dtype, device=matrix.device)
+            return torch.cat([matrix, pad], dim=0).contiguous()
+
+        gates = padded(tensors["if"])
+        bias = torch.zeros(gates.shape[0], dtype=torch.float32, device=gates.device)
+        bias[:2 * self.heads] = tensors["if.bias"].float()
+        self.projection, self.gate_projection = Linear(padded(tensors["qkvg"])), Linear(gates, bias)
+        self.out = Linear(tensors[n["o"]])
         self.norm = tensors[n["norm"]].float().contiguous()
 
     def cache_requests(self) -> list:
@@ -87,10 +95,11 @@ class MatrixMemory(Part):
         if not owns_cache:
             raise invalid_argument("a matrix-memory layer keeps a state of its own")
         plan = ctx.plan
-        projected = self.projection.forward(plain_rows(x))
+        x = plain_rows(x)
+        projected = self.projection.forward(x)
         qk, v = self.qk_width, self.v_width
-        gates = 2 * qk + 2 * v
-        coef = kernels.matrix_memory_gates(projected, gates, gates + self.heads, self.cap, views[1], heads=self.heads,
+        gates = self.gate_projection.forward(x, out_dtype=torch.float32)
+        coef = kernels.matrix_memory_gates(gates, 0, self.heads, self.cap, views[1], heads=self.heads,
                                            tables=ctx.tables, seqs=plan.n_seqs)
         read = kernels.scalar_recurrence(projected[:, qk:2 * qk], projected[:, :qk], projected[:, 2 * qk:2 * qk + v],
                                          coef, views[0], heads=self.heads, k_heads=self.heads, q_heads=self.heads,

@@ -10,7 +10,9 @@ causal convolution per channel (taps `conv`, a bias) and SiLU. Then per head, wi
 
 y (heads concatenated) is multiplied by silu(z), divided by its root mean square in `norm_groups` equal parts,
 multiplied by a weight [inner] and projected by W_o. What a sequence keeps, as fixed-size state per cache slot:
-S in 32-bit floats and the convolution's last taps - 1 inputs. Steps, decays, state, read-out and norm are 32-bit.
+S in 32-bit floats and the convolution's last taps - 1 inputs. Steps, decays, state, read-out and norm are 32-bit; so
+is the result of dt's projection (a product of its own, H rows), since its rounding would be multiplied by the decay rate
+inside an exponential.
 
 Parameters (`spec.params`): hidden_size, num_heads, vdim, state, groups, conv (taps), norm_groups, eps, and the
 tensor names under the prefix: in, conv, conv_bias, dt_bias, a_log, skip, norm, o.
@@ -58,6 +60,7 @@ class StateSpaceMixer(Part):
         self.width = 2 * self.inner + 2 * self.groups * self.state + self.heads
         self.names = {key: spec.param(key + "_name", default) for key, default in NAMES.items()}
         self.projection: Optional[Linear] = None
+        self.step_projection: Optional[Linear] = None
         self.out: Optional[Linear] = None
 
     def parameter_specs(self) -> List[ParamSpec]:
@@ -75,11 +78,14 @@ class StateSpaceMixer(Part):
 
     def bind(self, tensors) -> None:
         n = self.names
-        fused = tensors[n["in"]]
-        if self.width % 8:            # rows of the product's result start on 16-byte boundaries
-            pad = torch.zeros((8 - self.width % 8, self.hidden), dtype=fused.dtype, device=fused.device)
-            fused = torch.cat([fused, pad], dim=0).contiguous()
-        self.projection, self.out = Linear(fused), Linear(tensors[n["o"]])
+        def padded(matrix):        # rows of a product's result start on 16-byte boundaries
+            extra = -matrix.shape[0] % 8
+            pad = torch.zeros((extra, self.hidden), dtype=matrix.dtype, device=matrix.device)
+            return torch.cat([matrix, pad], dim=0).contiguous()
+
+        fused, main = tensors[n["in"]], self.width - self.heads
+        self.projection, self.step_projection = Linear(padded(fused[:main])), Linear(padded(fused[main:]))
+        self.out = Linear(tensors[n["o"]])
         # everything that enters the recurrence beside the projections is 32-bit
         for key in ("conv", "conv_bias", "dt_bias", "a_log", "skip", "norm"):
             setattr(self, key, tensors[n[key]].float().contiguous())
@@ -94,13 +100,14 @@ class StateSpaceMixer(Part):
         if not owns_cache:
             raise invalid_argument("a state-space layer keeps a state of its own")
         plan = ctx.plan
-        projected = self.projection.forward(plain_rows(x))
+        x = plain_rows(x)
+        projected = self.projection.forward(x)
+        steps = self.step_projection.forward(x, out_dtype=torch.float32)
         inner, span = self.inner, self.groups * self.state
         z = projected[:, :inner]
         mixed = kernels.short_conv(projected[:, inner:inner + self.channels], self.conv, self.conv_bias,
                                    views[1] if self.taps > 1 else None, silu=True, tables=ctx.tables, seqs=plan.n_seqs)
-        coef = kernels.state_space_gates(projected[:, inner + self.channels:inner + self.channels + self.heads],
-                                         self.dt_bias, self.a_log)
+        coef = kernels.state_space_gates(steps[:, :self.heads], self.dt_bias, self.a_log)
         values = mixed[:, :inner]
         read = kernels.scalar_recurrence(mixed[:, inner:inner + span], mixed[:, inner + span:], values, coef, views[0],
                                          heads=self.heads, k_heads=self.groups, q_heads=self.groups, dim=self.state,
