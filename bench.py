@@ -363,11 +363,11 @@ def biropel_shape(width: int, layers: int = 4) -> dict:
     half, half_groups = max(1, heads // 2), max(1, heads // 8)
     mlp = {"kind": "dense", "ff": 4 * width}
     base = {"heads": heads, "kv_heads": groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 4096},
-            "rot": {"base": 1000000.0, "dims": 64}}
+            "rot": {"base": 10000.0, "dims": 64}}
     stretched = {"heads": half, "kv_heads": half_groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                 "mask": {"size": 4096}, "softcap": 30.0, "rot": {"base": 500000.0, "dims": 128, "scaling": {
+                 "mask": {"size": 4096}, "softcap": 50.0, "rot": {"base": 100000.0, "dims": 128, "scaling": {
                      "factor": 8.0, "original": 1024.0, "fast": 32.0, "slow": 1.0}}}
-    unrotated = {"heads": half, "kv_heads": half_groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+    unrotated = {"heads": half, "kv_heads": half_groups, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
                  "q_temp": {"coef": 0.1, "every": 1024}}
     kinds = [
         lambda: {"type": "attention", "mixer": dict(base), "mlp": dict(mlp)},
@@ -375,7 +375,7 @@ def biropel_shape(width: int, layers: int = 4) -> dict:
         lambda: {"type": "parallel", "mixer": {"left": dict(stretched), "right": {
             "heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 8}}, "mlp": dict(mlp)},
         lambda: {"type": "parallel_2", "mixer": {"left": dict(unrotated), "right": {
-            "heads": half, "dim": 128, "vdim": 128, "gate_cap": 15.0}}, "mlp": dict(mlp)},
+            "heads": half, "dim": 128, "vdim": 128, "gate_cap": 20.0}}, "mlp": dict(mlp)},
     ]
     stack = []
     for index in range(layers):

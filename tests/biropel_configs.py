@@ -80,7 +80,7 @@ SMALL_B = model(131, 72, 3e-6, [
     state_space_layer(attention(2, 2, 12, 20, 0.3, window=17, rot=(300.0, 4), scaling=(2.0, 32.0, 4.0, 0.5),
                                 softcap=10.0), heads=3, vdim=8, state=5, groups=3, conv=1, norm_groups=1, ff=24),
     attention_layer(attention(6, 3, 12, 8, 0.3, window=64, rot=(1000.0, 12)), ff=72),
-    state_space_layer(attention(3, 3, 8, 8, 0.4, window=100, rot=(50.0, 8), softcap=30.0), heads=2, vdim=20,
+    state_space_layer(attention(3, 3, 8, 8, 0.4, window=100, rot=(50.0, 8), softcap=35.0), heads=2, vdim=20,
                       state=12, groups=1, conv=2, norm_groups=4),
     attention_layer(attention(3, 3, 12, 8, 0.2, window=30, rot=(1000.0, 12), kv_from=2), ff=16),
     attention_layer(attention(6, 3, 12, 8, 0.3, rot=(1000.0, 12), kv_from=2)),
@@ -91,15 +91,15 @@ PLAIN = model(61, 48, 1e-6, [
     state_space_layer(attention(2, 1, 16, 16, 0.3, window=50, rot=(100.0, 16), softcap=20.0), heads=2, vdim=16,
                       state=16, groups=1, conv=3, norm_groups=1, ff=64),
     attention_layer(attention(2, 2, 16, 16, 0.3, window=30, rot=(100.0, 8)), ff=32),
-    matrix_memory_layer(attention(2, 1, 16, 16, 0.25, softcap=30.0, q_temp=(0.5, 32)), heads=2, dim=16, vdim=16,
+    matrix_memory_layer(attention(2, 1, 16, 16, 0.25, softcap=28.0, q_temp=(0.5, 32)), heads=2, dim=16, vdim=16,
                         gate_cap=8.0, ff=32),
 ], positions=600)
 
 # a single lane (the mixing matrix is one number)
 ONE_LANE = model(53, 40, 1e-5, [
     attention_layer(attention(2, 1, 8, 16, 0.35, window=25, rot=(100.0, 8)), ff=24),
-    matrix_memory_layer(attention(2, 2, 8, 8, 0.35, softcap=30.0, q_temp=(0.3, 10)), heads=2, dim=8, vdim=8,
-                        gate_cap=15.0, ff=24),
+    matrix_memory_layer(attention(2, 2, 8, 8, 0.35, softcap=22.0, q_temp=(0.3, 10)), heads=2, dim=8, vdim=8,
+                        gate_cap=9.0, ff=24),
 ], streams=1, positions=600)
 
 # widths that the tensor-core kernels take: heads of 64 and 128 with groups of 4, 1 and 2 heads, a window whose edge
@@ -107,11 +107,11 @@ ONE_LANE = model(53, 40, 1e-5, [
 WIDE = model(211, 256, 1e-5, [
     attention_layer(attention(8, 2, 64, 64, 0.15, window=150, rot=(10000.0, 32)), ff=256),
     state_space_layer(attention(4, 4, 64, 64, 0.15, window=100, rot=(20000.0, 64), scaling=(8.0, 128.0, 16.0, 1.0),
-                                softcap=30.0), heads=8, vdim=32, state=64, groups=2, conv=4, norm_groups=2, ff=128),
+                                softcap=25.0), heads=8, vdim=32, state=64, groups=2, conv=4, norm_groups=2, ff=128),
     attention_layer(attention(8, 2, 64, 64, 0.15, window=70, rot=(10000.0, 32), kv_from=0), ff=128),
     attention_layer(attention(2, 1, 128, 128, 0.1, rot=(50000.0, 64))),
-    matrix_memory_layer(attention(4, 2, 64, 64, 0.12, softcap=30.0, q_temp=(0.3, 256)), heads=4, dim=64, vdim=64,
-                        gate_cap=15.0, ff=256),
+    matrix_memory_layer(attention(4, 2, 64, 64, 0.12, softcap=25.0, q_temp=(0.25, 128)), heads=4, dim=64, vdim=64,
+                        gate_cap=12.0, ff=256),
 ], streams=4, positions=1300)
 
 ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "plain": PLAIN, "one_lane": ONE_LANE, "wide": WIDE}
