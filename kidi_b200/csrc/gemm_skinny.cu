@@ -48,7 +48,8 @@ struct Epilogue {
     long long ld_normed;
     float* parts_out;
     int parts_stride;
-    int gelu;                     // the plain store writes gelu(y + bias), the exact (erf) form, instead of y + bias
+    int gelu;                     // the plain store writes an activation of y + bias instead of y + bias: 1 the exact
+                                  // (erf) gelu, 2 the squared relu max(y + bias, 0)^2
 };
 
 __device__ __forceinline__ uint4 load_streaming(const void* pointer) {
@@ -246,7 +247,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TY* _
             for (int offset = span / 2; offset > 0; offset >>= 1) square += __shfl_xor_sync(0xffffffffu, square, offset);
             if (r == 0 && m < M) e.parts_out[(long long)m * e.parts_stride + blockIdx.x] = square;
         } else if (inside) {
-            if (!GATED && e.gelu) sum = 0.5f * sum * (1.0f + erff(sum * 0.70710678118654752440f));
+            if (!GATED && e.gelu == 1) sum = 0.5f * sum * (1.0f + erff(sum * 0.70710678118654752440f));
+            if (!GATED && e.gelu == 2) sum = fmaxf(sum, 0.f) * fmaxf(sum, 0.f);
             y[m * ldy + n0 + r] = from_float<TY>(sum);
         }
     }
@@ -295,7 +297,8 @@ struct KidiSkinnyExtras {          // every pointer may be null: the plain produ
     long long ld_normed;
     float* parts_out;
     int parts_stride;
-    int gelu;                      // not gated, not into the residual: the result passes the exact gelu
+    int gelu;                      // not gated, not into the residual: the result passes the exact gelu (1) or the
+                                   // squared relu (2)
 };
 
 // How many parts per row the product into the residual writes for N features.

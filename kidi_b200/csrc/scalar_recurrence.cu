@@ -346,6 +346,30 @@ __global__ void short_conv_state_kernel(ShortConvArgs a) {
     for (int j = 0; j < reach; ++j) state[(long long)j * a.channels + c] = kept[j];
 }
 
+// One token a sequence (decoding): the output and the state's shift in one kernel, a thread a (sequence, channel); every
+// earlier input comes from the state.
+template <typename T>
+__global__ void short_conv_step_kernel(ShortConvArgs a) {
+    const long long index = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= (long long)a.seqs * a.channels) return;
+    const int seq = (int)(index / a.channels), c = (int)(index - (long long)seq * a.channels);
+    const int row = a.seq_row0[seq];
+    if (a.seq_len[seq] <= 0 || a.row_seq[row] < 0) return;
+    const int reach = a.taps - 1;
+    T* state = (T*)a.state + (long long)a.seq_slot[seq] * reach * a.channels;
+    T kept[MAX_TAPS];
+    float sum = a.bias ? a.bias[c] : 0.f;
+    for (int j = 0; j < reach; ++j) {
+        kept[j] = state[(long long)j * a.channels + c];
+        sum = fmaf(a.weight[(long long)c * a.taps + j], to_float(kept[j]), sum);
+    }
+    const T x = ((const T*)a.x)[(long long)row * a.ldx + c];
+    sum = fmaf(a.weight[(long long)c * a.taps + reach], to_float(x), sum);
+    ((T*)a.out)[(long long)row * a.ldo + c] = from_float<T>(a.silu ? silu(sum) : sum);
+    for (int j = 0; j + 1 < reach; ++j) state[(long long)j * a.channels + c] = kept[j + 1];
+    if (reach > 0) state[(long long)(reach - 1) * a.channels + c] = x;
+}
+
 // ---------------------------------------------------------------- the state-space mixer's gates and finish
 // coef[row, head] = (exp(-exp(A_log) dt), dt), dt = softplus(dt~ + bias) (no clamp).
 template <typename T>
@@ -494,6 +518,16 @@ KIDI_API int kidi_short_conv_state(const ShortConvArgs* args, int dtype, cudaStr
     const unsigned blocks = (unsigned)(((long long)a.seqs * a.channels + 255) / 256);
     if (dtype == KIDI_F32) return kidi_launch(short_conv_state_kernel<float>, blocks, 256, 0, stream, a);
     if (dtype == KIDI_BF16) return kidi_launch(short_conv_state_kernel<bf16>, blocks, 256, 0, stream, a);
+    return KIDI_REFUSED_DTYPE;
+}
+
+KIDI_API int kidi_short_conv_step(const ShortConvArgs* args, int dtype, cudaStream_t stream) {
+    const ShortConvArgs& a = *args;
+    if (a.seqs <= 0) return 0;
+    if (a.channels <= 0 || a.taps < 1 || a.taps > MAX_TAPS) return KIDI_REFUSED_SIZE;
+    const unsigned blocks = (unsigned)(((long long)a.seqs * a.channels + 255) / 256);
+    if (dtype == KIDI_F32) return kidi_launch(short_conv_step_kernel<float>, blocks, 256, 0, stream, a);
+    if (dtype == KIDI_BF16) return kidi_launch(short_conv_step_kernel<bf16>, blocks, 256, 0, stream, a);
     return KIDI_REFUSED_DTYPE;
 }
 

@@ -42,6 +42,7 @@ def library():
         lib.kidi_scalar_recurrence.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_short_conv.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_short_conv_state.argtypes = [c_void_p, c_int, c_void_p]
+        lib.kidi_short_conv_step.argtypes = [c_void_p, c_int, c_void_p]
         lib.kidi_state_space_gates.argtypes = [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                c_void_p]
         lib.kidi_state_space_finish.argtypes = [c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p,
@@ -51,8 +52,9 @@ def library():
                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.kidi_matrix_memory_finish.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p,
                                                   c_longlong, c_int, c_int, c_int, c_float, c_void_p]
-        for name in ("kidi_scalar_recurrence", "kidi_short_conv", "kidi_short_conv_state", "kidi_state_space_gates",
-                     "kidi_state_space_finish", "kidi_matrix_memory_gates", "kidi_matrix_memory_finish"):
+        for name in ("kidi_scalar_recurrence", "kidi_short_conv", "kidi_short_conv_state", "kidi_short_conv_step",
+                     "kidi_state_space_gates", "kidi_state_space_finish", "kidi_matrix_memory_gates",
+                     "kidi_matrix_memory_finish"):
             getattr(lib, name).restype = c_int
         _library = lib
     return _library
@@ -99,11 +101,12 @@ def scalar_recurrence(k: torch.Tensor, q: torch.Tensor, v: torch.Tensor, coef: t
 
 
 def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], *,
-               silu: bool, tables, seqs: int) -> torch.Tensor:
+               silu: bool, tables, seqs: int, one_token: bool = False) -> torch.Tensor:
     """A causal convolution over time on every channel of x [rows, channels] (a view of the step's element type):
     y_t = bias + sum_j weight[c, j] x_(t - taps + 1 + j), then SiLU if asked; inputs of earlier steps come from
     `state` [slots + 1, taps - 1, channels] (the step's element type), which then takes the sequence's last
-    taps - 1 inputs. weight float32 [channels, taps], bias float32 [channels] or None."""
+    taps - 1 inputs. weight float32 [channels, taps], bias float32 [channels] or None. `one_token`: every sequence
+    of the step brings one token (decoding): result and state in one kernel."""
     ops._need_cuda(x, weight, bias, state)
     _rows_view(x, "short convolution")
     rows, channels = x.shape
@@ -122,6 +125,9 @@ def short_conv(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
                          tables.seq_slot.data_ptr(), tables.seq_start.data_ptr(), tables.seq_row0.data_ptr(),
                          tables.seq_len.data_ptr(), rows, seqs, channels, taps, 1 if silu else 0)
     lib = library()
+    if one_token and taps > 1:
+        _check(lib.kidi_short_conv_step(ctypes.byref(args), dtype_code(x.dtype), ops._stream()), "short_conv[one token]")
+        return out
     _check(lib.kidi_short_conv(ctypes.byref(args), dtype_code(x.dtype), ops._stream()), "short_conv")
     if taps > 1:
         _check(lib.kidi_short_conv_state(ctypes.byref(args), dtype_code(x.dtype), ops._stream()), "short_conv_state")

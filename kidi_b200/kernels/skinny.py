@@ -83,7 +83,8 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
     """y = x @ weight.T (+ bias, float32) for x [M <= 64, K], weight [N, K], both bfloat16. With
     `factors` = (parts, width, eps) every row m of the result is multiplied by
     1 / sqrt(sum(parts[m]) / width + eps) first (the factor that an RMSNorm left out of x).
-    `activation` "gelu": the result passes the exact (erf) gelu in the epilogue, in 32-bit."""
+    `activation` "gelu": the result passes the exact (erf) gelu in the epilogue, in 32-bit; "relu_squared":
+    max(y, 0)^2 likewise."""
     _need_cuda(x, weight, bias)
     ops.check_bias(bias, weight.shape[0])
     if not supports(x, weight) or x.shape[1] != weight.shape[1]:
@@ -92,15 +93,15 @@ def gemm(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, out: Opt
     N = weight.shape[0]
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
-    if activation not in (None, "gelu"):
-        raise invalid_argument("gemm_skinny: the epilogue knows the activation 'gelu' only")
+    if activation not in (None, "gelu", "relu_squared"):
+        raise invalid_argument("gemm_skinny: the epilogue knows the activations 'gelu' and 'relu_squared' only")
     extras = Extras()
     _factor_fields(extras, factors)
-    extras.gelu = int(activation == "gelu")
+    extras.gelu = {None: 0, "gelu": 1, "relu_squared": 2}[activation]
     _check(_library().kidi_gemm_skinny(_ptr(x), _ptr(weight), _ptr(out), dtype_code(out.dtype), M, N, K, x.stride(0),
                                        weight.stride(0), out.stride(0), 0, row_tiles or _row_tiles(N, M, x.device), _ptr(bias),
                                        ctypes.byref(extras), _stream()),
-           "gemm_gelu[skinny]" if activation else "gemm_skinny[row factors]" if factors is not None else "gemm_skinny")
+           f"gemm_{activation}[skinny]" if activation else "gemm_skinny[row factors]" if factors is not None else "gemm_skinny")
     return out
 
 

@@ -125,7 +125,11 @@ class DenseFeedForward(Part):
             self.coefficients = tensors[self.act_name].float().contiguous()
 
     def forward(self, x, ctx, sink=None) -> Optional[torch.Tensor]:
-        z = self.up.forward(x)
         if self.activation == "relu_squared":
+            from ..kernels import skinny
+            if self.up.bias is None and skinny.fits(x, self.up.weight):     # few rows: the activation in the epilogue
+                return self.down.forward(skinny.gemm(x, self.up.weight, x.dtype, activation="relu_squared"))
+            z = self.up.forward(x)
             return self.down.forward(ops.relu_squared(z, out=z))
+        z = self.up.forward(x)
         return self.down.forward(ops.poly_norm(z, self.coefficients, self.eps))

@@ -106,7 +106,8 @@ class StateSpaceMixer(Part):
         inner, span = self.inner, self.groups * self.state
         z = projected[:, :inner]
         mixed = kernels.short_conv(projected[:, inner:inner + self.channels], self.conv, self.conv_bias,
-                                   views[1] if self.taps > 1 else None, silu=True, tables=ctx.tables, seqs=plan.n_seqs)
+                                   views[1] if self.taps > 1 else None, silu=True, tables=ctx.tables, seqs=plan.n_seqs,
+                                   one_token=plan.is_decode)
         coef = kernels.state_space_gates(steps[:, :self.heads], self.dt_bias, self.a_log)
         values = mixed[:, :inner]
         read = kernels.scalar_recurrence(mixed[:, inner:inner + span], mixed[:, inner + span:], values, coef, views[0],
