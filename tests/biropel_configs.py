@@ -6,7 +6,7 @@ part of a head and of a whole head, stretched and plain frequencies, windows sho
 page, exactly a page and none, layers that read another layer's keys (the next layer, a later one, two layers
 reading the same one), one to four residual lanes and none, state-space mixers with one to several groups, norm
 parts and convolution taps (also one tap: no carried inputs), matrix memories of one to several heads, layers
-without a feed-forward. `tensors(config, seed)` draws every tensor under its checkpoint name.
+without a feed-forward, a width that is no multiple of four. `tensors(config, seed)` draws every tensor under its checkpoint name.
 """
 import torch
 
@@ -114,7 +114,15 @@ WIDE = model(211, 256, 1e-5, [
                         gate_cap=12.0, ff=256),
 ], streams=4, positions=1300)
 
-ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "plain": PLAIN, "one_lane": ONE_LANE, "wide": WIDE}
+# a width that is no multiple of four (no kernel takes its rows in pieces of several elements), three lanes
+ODD = model(71, 50, 1e-5, [
+    attention_layer(attention(2, 1, 10, 6, 0.3, window=45, rot=(100.0, 6)), ff=30),
+    state_space_layer(attention(3, 1, 6, 10, 0.3, window=20, rot=(100.0, 6), softcap=12.0), heads=3, vdim=6, state=7,
+                      groups=1, conv=3, norm_groups=3, ff=22),
+    matrix_memory_layer(attention(2, 2, 6, 6, 0.3, softcap=12.0, q_temp=(0.3, 9)), heads=3, dim=7, vdim=5, gate_cap=7.0),
+], streams=3, positions=600)
+
+ALL = {"small_a": SMALL_A, "small_b": SMALL_B, "plain": PLAIN, "one_lane": ONE_LANE, "wide": WIDE, "odd": ODD}
 
 
 def single(layer, vocab=67, width=48, eps=1e-5, streams=None, positions=900):

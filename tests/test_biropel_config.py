@@ -148,3 +148,23 @@ def test_plain_recurrences_against_their_sums():
         y = y * torch.nn.functional.silu(z[t])
         want[t] = y / torch.sqrt((y * y).mean() + 1e-6)
     assert torch.allclose(got, want, atol=1e-10)
+
+
+def test_the_command_line_writes_and_inspects_a_folder(tmp_path, capsys):
+    """`random-model` draws every declared tensor (the lanes' mixing matrices near the identity) and `inspect` reads
+    the folder back; neither needs a GPU."""
+    import json
+
+    import kidi_b200
+    from safetensors import safe_open
+    (tmp_path / "config.json").write_text(json.dumps(biropel_configs.SMALL_B))
+    folder = tmp_path / "model"
+    assert kidi_b200.main(["random-model", "--config", str(tmp_path / "config.json"), "-o", str(folder), "--seed", "4"]) == 0
+    assert kidi_b200.main(["inspect", "-m", str(folder)]) == 0
+    printed = capsys.readouterr().out
+    assert "architecture: Biropel" in printed and "layers: 6 (run order: 6 entries)" in printed
+    with safe_open(str(folder / "model.safetensors"), "pt") as handle:
+        names = set(handle.keys())
+        mixing = handle.get_tensor("l0.hc1.mix").float()
+    assert names == set(biropel_configs.tensors(biropel_configs.SMALL_B, 0))
+    assert mixing.shape == (3, 3) and float((mixing - torch.eye(3)).abs().max()) < 0.6
